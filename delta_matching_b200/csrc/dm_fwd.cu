@@ -1,0 +1,292 @@
+// Forward of delta-matching fp8 attention on sm_100a: S = Q8 K8^T on tcgen05 (kind::f8f6f4) with the accumulator in TMEM,
+// per-(row, 32-key block) power-of-two P basis, P codes and UE8M0 scale words written back to TMEM, O += P V as one
+// block-scaled tcgen05 chain (kind::mxf8f6f4), O bf16 and natural-log LSE.
+//
+// Numerics follow the reference's Blackwell contract ("sm100-mx"): delta_matching/reference.py:159-171 (mx_pfwd),
+// :454-471 (forward engine) and the op list in delta_matching/sm100/dm_fwd_sm100.py:3685-3757:
+//   c_b = (qs * log2e) * ks_b;  xb = max_b(S_acc) * c_b;  k_b = max(floor(xb), -1e30);  p = ex2(fma(S_acc, c_b, 7 - k_b))
+//   code = e4m3(p);  m integer-valued running max (ceil), moved only when the candidate exceeds it by more than 32;
+//   SFA_b = UE8M0(k_b - 7 - m), SFB_b = V scale byte;  l += sum_b (sum of the unquantised p of block b) * 2^(k_b - 7 - m)
+//   O = bf16(O_acc / l);  LSE = (m + log2 l) * ln2.  Key tiles are visited from the highest index down.
+//
+// CTA = one 128-query tile of one (batch, query head).  Warps 0-3: softmax / epilogue (thread t owns TMEM lane t = query
+// row t).  Warp 4: TMA producer.  Warp 5: MMA issuer and TMEM owner.  Every mbarrier wait is bounded.
+#include <cuda_bf16.h>
+#include "dm_common.cuh"
+#include "dm_kernels.h"
+
+namespace dm {
+
+template <int D>
+struct FwdCfg {
+  static constexpr int kSub = D / 128;                 // 128-byte-wide sub-tiles per operand row
+  static constexpr int kTileBytes = 128 * D;           // one 128-row operand tile
+  static constexpr int kStages = 2;
+  static constexpr int kTmemCols = (D == 128) ? 256 : 512;
+  static constexpr int kColS = 0;                      // S accumulator, 128 fp32 columns; P codes reuse columns 0-31
+  static constexpr int kColSfa = 32;                   // 4 columns, each this row's SFA word
+  static constexpr int kColSfb = 36;                   // 4 columns, each the tile's V scale word
+  static constexpr int kColO = 128;                    // O accumulator, D fp32 columns
+  // shared memory: Q | K stages | V stages | barriers
+  static constexpr int kSmemQ = 0;
+  static constexpr int kSmemK = kTileBytes;
+  static constexpr int kSmemV = kSmemK + kStages * kTileBytes;
+  static constexpr int kSmemBar = kSmemV + kStages * kTileBytes;
+  static constexpr int kSmemBytes = kSmemBar + 256 + 1024;   // + slack for the 1024-byte alignment of the tile base
+};
+
+template <int D>
+__global__ void __launch_bounds__(192, (D == 128) ? 2 : 1)
+fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+           const __grid_constant__ CUtensorMap tm_v, const FwdParams p) {
+  using C = FwdCfg<D>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem + C::kSmemQ;
+  uint8_t* sK = smem + C::kSmemK;
+  uint8_t* sV = smem + C::kSmemV;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kSmemBar);
+  uint64_t* bar_q = bars + 0;
+  uint64_t* bar_s = bars + 1;     // S accumulator ready (MMA commit)
+  uint64_t* bar_p = bars + 2;     // P codes + scale words written (128 arrivals)
+  uint64_t* bar_o = bars + 3;     // PV chain done (MMA commit)
+  uint64_t* full_k = bars + 4;    // [kStages]
+  uint64_t* full_v = bars + 6;    // [kStages]
+  uint64_t* empty = bars + 8;     // [kStages] stage free again (MMA commit)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 13);
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int n_qt = p.N / 128;
+  const int qt = n_qt - 1 - static_cast<int>(blockIdx.x);      // heavy (long-row) tiles first when causal
+  const int bh = blockIdx.y;
+  const int b = bh / p.H, h = bh % p.H;
+  const int hk = h / (p.H / p.Hk);
+  const int bhk = b * p.Hk + hk;
+  const int n_it = p.causal ? (qt + 1) : n_qt;                  // key tiles visited, highest index first
+  const int kt_first = p.causal ? qt : (n_qt - 1);
+
+  if (tid == 0) {
+    mbar_init(bar_q, 1);
+    mbar_init(bar_s, 1);
+    mbar_init(bar_p, 128);
+    mbar_init(bar_o, 1);
+    for (int s = 0; s < C::kStages; ++s) {
+      mbar_init(full_k + s, 1);
+      mbar_init(full_v + s, 1);
+      mbar_init(empty + s, 1);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 5) {
+    tmem_alloc(tmem_slot, C::kTmemCols);
+    tmem_relinquish();
+    tc_fence_before();
+  }
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp == 4) {
+    // ------------------------------------------------------------------------------------------ TMA producer
+    if (elect_one()) {
+      tma_prefetch_desc(&tm_q);
+      tma_prefetch_desc(&tm_k);
+      tma_prefetch_desc(&tm_v);
+      mbar_expect_tx(bar_q, C::kTileBytes);
+      for (int s = 0; s < C::kSub; ++s) tma_load_2d(sQ + s * 16384, &tm_q, bar_q, s * 128, bh * p.N + qt * 128);
+      for (int it = 0; it < n_it; ++it) {
+        const int st = it % C::kStages;
+        if (it >= C::kStages) {
+          if (!wait_or_abort(empty + st, ((it / C::kStages) - 1) & 1, abort_flag)) {
+            raise_abort(abort_flag, p.status, kStatusTimeoutProducer);
+            break;
+          }
+        }
+        const int row = bhk * p.N + (kt_first - it) * 128;
+        mbar_expect_tx(full_k + st, C::kTileBytes);
+        for (int s = 0; s < C::kSub; ++s)
+          tma_load_2d(sK + st * C::kTileBytes + s * 16384, &tm_k, full_k + st, s * 128, row);
+        mbar_expect_tx(full_v + st, C::kTileBytes);
+        for (int s = 0; s < C::kSub; ++s)
+          tma_load_2d(sV + st * C::kTileBytes + s * 16384, &tm_v, full_v + st, s * 128, row);
+      }
+    }
+  } else if (warp == 5) {
+    // ------------------------------------------------------------------------------------------ MMA issuer
+    if (elect_one()) {
+      constexpr uint32_t kIdescS = idesc_f8(128, 128, false, false);
+      bool ok = wait_or_abort(bar_q, 0, abort_flag);
+      for (int it = 0; ok && it < n_it; ++it) {
+        const int st = it % C::kStages;
+        const uint32_t ph = (it / C::kStages) & 1;
+        if (!(ok = wait_or_abort(full_k + st, ph, abort_flag))) break;
+        tc_fence_after();
+        // S = Q K^T: both operands K-major, k-step of 32 bytes inside the 128-byte swizzle row
+#pragma unroll
+        for (int ks = 0; ks < D / 32; ++ks) {
+          const uint32_t off = (ks / 4) * 16384 + (ks % 4) * 32;
+          mma_f8_ss(tmem + C::kColS, smem_desc_sw128(smem_u32(sQ) + off, 16, 1024),
+                    smem_desc_sw128(smem_u32(sK + st * C::kTileBytes) + off, 16, 1024), kIdescS, ks > 0);
+        }
+        tc_commit(bar_s);
+        if (!(ok = wait_or_abort(bar_p, it & 1, abort_flag))) break;
+        if (!(ok = wait_or_abort(full_v + st, ph, abort_flag))) break;
+        tc_fence_after();
+        // O += P V: A = P codes in TMEM (8 columns per 32-key step), B = V tile MN-major (32 key rows per step)
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) {
+#pragma unroll
+          for (int s = 0; s < C::kSub; ++s) {
+            mma_mxf8_ts(tmem + C::kColO + s * 128, tmem + C::kColS + ks * 8,
+                        smem_desc_sw128(smem_u32(sV + st * C::kTileBytes) + s * 16384 + ks * 4096, 16, 1024),
+                        idesc_mxf8(128, 128, false, true, ks, ks), tmem + C::kColSfa, tmem + C::kColSfb,
+                        (it > 0) || (ks > 0));
+          }
+        }
+        tc_commit(empty + st);
+        tc_commit(bar_o);
+        // the next S overwrites the P codes and scale words this chain still reads: wait for it
+        if (!(ok = wait_or_abort(bar_o, it & 1, abort_flag))) break;
+      }
+      if (!ok) raise_abort(abort_flag, p.status, kStatusTimeoutMma);
+    }
+  } else {
+    // ------------------------------------------------------------------------------------------ softmax / epilogue
+    const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+    const int row = qt * 128 + tid;                                       // query index inside the head
+    const int nblk = p.N / 32;
+    const float qsl = p.qs[static_cast<size_t>(bh) * nblk + row / 32] * kLog2e;
+    float m = 0.f, l = 0.f;
+    bool ok = true;
+    for (int it = 0; it < n_it; ++it) {
+      const int kt = kt_first - it;
+      const float4 ks4 = *reinterpret_cast<const float4*>(p.ks + static_cast<size_t>(bhk) * nblk + kt * 4);
+      const float4 vs4 = *reinterpret_cast<const float4*>(p.vs + static_cast<size_t>(bhk) * nblk + kt * 4);
+      const float cb[4] = {qsl * ks4.x, qsl * ks4.y, qsl * ks4.z, qsl * ks4.w};
+      const uint32_t sfb = pack4(scale_to_sb(vs4.x), scale_to_sb(vs4.y), scale_to_sb(vs4.z), scale_to_sb(vs4.w));
+      const bool diag = p.causal && (kt == qt);
+      if (!(ok = wait_warp(bar_s, it & 1, abort_flag))) break;
+      tc_fence_after();
+      float bsum[4], kb[4], bmax[4];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld32(tmem + lane_base + C::kColS + 32 * c, r);
+        tmem_wait_ld();
+        float s[32];
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+          s[e] = __uint_as_float(r[e]);
+          if (diag && (32 * c + e > tid)) s[e] = -INFINITY;
+        }
+        float mx = s[0];
+#pragma unroll
+        for (int e = 1; e < 32; ++e) mx = fmaxf(mx, s[e]);
+        bmax[c] = mx * cb[c];
+        kb[c] = fmaxf(floorf(bmax[c]), -1e30f);
+        const float bias = 7.0f - kb[c];
+        float sum = 0.f;
+        uint32_t codes[8];
+#pragma unroll
+        for (int e = 0; e < 32; e += 4) {
+          const float p0 = ex2_approx(fmaf(s[e + 0], cb[c], bias));
+          const float p1 = ex2_approx(fmaf(s[e + 1], cb[c], bias));
+          const float p2 = ex2_approx(fmaf(s[e + 2], cb[c], bias));
+          const float p3 = ex2_approx(fmaf(s[e + 3], cb[c], bias));
+          sum += (p0 + p1) + (p2 + p3);
+          codes[e / 4] = cvt_e4m3x4(p0, p1, p2, p3);
+        }
+        bsum[c] = sum;
+        tmem_st8(tmem + lane_base + C::kColS + 8 * c, codes);
+      }
+      const float mcand = ceilf(fmaxf(fmaxf(bmax[0], bmax[1]), fmaxf(bmax[2], bmax[3])));
+      float acc_scale = 1.0f;
+      if (it == 0) {
+        m = mcand;
+      } else if (mcand > m + 32.0f) {
+        acc_scale = sb_to_scale(static_cast<uint32_t>(max(0, min(__float2int_rn(m - mcand) + 127, 254))));
+        m = mcand;
+      }
+      if (it > 0 && __any_sync(0xffffffffu, acc_scale != 1.0f)) {
+        // rare: the running max moved by more than 32 binades; rescale this warp's O rows in place
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld32(tmem + lane_base + C::kColO + 32 * c, r);
+          tmem_wait_ld();
+#pragma unroll
+          for (int e = 0; e < 32; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) * acc_scale);
+          tmem_st32(tmem + lane_base + C::kColO + 32 * c, r);
+        }
+      }
+      l *= acc_scale;
+      uint32_t sb[4];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int e = __float2int_rn(kb[c] - 7.0f - m);      // saturates for fully masked blocks
+        sb[c] = static_cast<uint32_t>(max(0, min(max(e, -1000) + 127, 254)));
+        l = fmaf(bsum[c], __uint_as_float(sb[c] << 23), l);
+      }
+      const uint32_t sfa = pack4(sb[0], sb[1], sb[2], sb[3]);
+      tmem_st4(tmem + lane_base + C::kColSfa, sfa, sfa, sfa, sfa);
+      tmem_st4(tmem + lane_base + C::kColSfb, sfb, sfb, sfb, sfb);
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(bar_p);
+    }
+    if (ok) ok = wait_warp(bar_o, (n_it - 1) & 1, abort_flag);
+    if (!ok) {
+      raise_abort(abort_flag, p.status, kStatusTimeoutCompute);
+    } else {
+      tc_fence_after();
+      const float inv_l = 1.0f / l;
+      __nv_bfloat16* orow = p.o + static_cast<int64_t>(b) * p.o_sb + static_cast<int64_t>(row) * p.o_sn +
+                            static_cast<int64_t>(h) * p.o_sh;
+#pragma unroll 1
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(tmem + lane_base + C::kColO + 32 * c, r);
+        tmem_wait_ld();
+        uint32_t w[16];
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+          __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(r[2 * e]) * inv_l, __uint_as_float(r[2 * e + 1]) * inv_l);
+          w[e] = *reinterpret_cast<uint32_t*>(&v);
+        }
+        uint4* dst = reinterpret_cast<uint4*>(orow + 32 * c);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) dst[e] = make_uint4(w[4 * e], w[4 * e + 1], w[4 * e + 2], w[4 * e + 3]);
+      }
+      p.lse[static_cast<size_t>(bh) * p.N + row] = (m + log2f(l)) * kLn2;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 5) tmem_dealloc(tmem, C::kTmemCols);
+}
+
+template <int D>
+static cudaError_t launch_fwd_t(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FwdParams& p,
+                                cudaStream_t stream) {
+  using C = FwdCfg<D>;
+  static bool attr_set[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(fwd_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+    if (e != cudaSuccess) return e;
+    attr_set[dev] = true;
+  }
+  dim3 grid(p.N / 128, p.B * p.H);
+  fwd_kernel<D><<<grid, 192, C::kSmemBytes, stream>>>(tq, tk, tv, p);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_fwd(int D, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FwdParams& p,
+                       cudaStream_t stream) {
+  return D == 128 ? launch_fwd_t<128>(tq, tk, tv, p, stream) : launch_fwd_t<256>(tq, tk, tv, p, stream);
+}
+
+}  // namespace dm

@@ -1,0 +1,88 @@
+// Internal launch interface between the C-ABI layer (dm_abi.cu) and the kernel translation units.
+#pragma once
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace dm {
+
+// Codes are e4m3 bytes in (B, H, N, D) order, dense; scales fp32 powers of two in (B, H, N / 32) order.
+struct FwdParams {
+  const float* qs;
+  const float* ks;
+  const float* vs;
+  __nv_bfloat16* o;            // element strides for (batch, token, head); head_dim is contiguous
+  int64_t o_sb, o_sn, o_sh;
+  float* lse;                  // (B, H, N) natural log
+  int B, H, Hk, N;
+  int causal;
+  int* status;
+};
+
+struct DeltaParams {
+  const float* qs;
+  const float* ks;
+  const float* vs;
+  const float* dos;
+  const float* lse;            // (B, H, N)
+  float* delta;                // (B, H, N)
+  int B, H, Hk, N;
+  int causal;
+  int* status;
+};
+
+struct BwdParams {
+  const float* qs;
+  const float* ks;
+  const float* vs;
+  const float* dos;
+  const float* lse;            // (B, H, N)
+  const float* delta;          // (B, H, N)
+  __nv_bfloat16* dq;           // (batch, token, head) element strides, head_dim contiguous; dq has H heads
+  int64_t dq_sb, dq_sn, dq_sh;
+  __nv_bfloat16* dk;           // Hk heads
+  int64_t dk_sb, dk_sn, dk_sh;
+  __nv_bfloat16* dv;
+  int64_t dv_sb, dv_sn, dv_sh;
+  float* rowsum_ds;            // optional (B, H, N): sum_j dS_ij before quantisation (identity probe); may be null
+  float* sum_abs_pdp;          // optional (B, H, N): sum_j |P_ij dP_ij|; may be null
+  float sm_scale;
+  int B, H, Hk, N;
+  int causal;
+  int* status;
+};
+
+struct QuantParams {
+  const __nv_bfloat16* x;      // element strides for (batch, head, token); head_dim contiguous
+  int64_t sb, sh, sn;
+  const float* mean;           // optional (B, H, D): subtracted before the prescale
+  const __nv_bfloat16* o;      // optional, same logical shape as x with its own strides: stale delta = sum_d x * o
+  int64_t o_sb, o_sh, o_sn;
+  float prescale;
+  uint8_t* codes;              // (B, H, N, D)
+  float* scales;               // (B, H, N / 32)
+  float* delta;                // optional (B, H, N)
+  int B, H, N, D;
+};
+
+struct KMeanParams {
+  const __nv_bfloat16* k;
+  int64_t sb, sh, sn;
+  float* partial;              // (B * Hk, N / 64, D) scratch
+  float* mean;                 // (B, Hk, D)
+  int B, Hk, N, D;
+};
+
+cudaError_t launch_fwd(int D, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FwdParams& p,
+                       cudaStream_t stream);
+cudaError_t launch_delta(int D, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
+                         const CUtensorMap& tdo, const DeltaParams& p, cudaStream_t stream);
+cudaError_t launch_bwd_dkdv(int D, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
+                            const CUtensorMap& tdo, const BwdParams& p, cudaStream_t stream);
+cudaError_t launch_bwd_dq(int D, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
+                          const CUtensorMap& tdo, const BwdParams& p, cudaStream_t stream);
+cudaError_t launch_quant(const QuantParams& p, cudaStream_t stream);
+cudaError_t launch_kmean(const KMeanParams& p, cudaStream_t stream);
+
+}  // namespace dm

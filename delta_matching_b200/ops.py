@@ -1,0 +1,244 @@
+"""The op layer: torch tensors in, torch tensors out, the work done by the C ABI (include/dm_b200.h).
+
+These functions take the place of `torch.ops.delta_matching.{fwd_fp8, delta_fp8, bwd_fp8_t}` (schemas at
+csrc/delta_matching_api.cpp:683-715) and of the producers `quant_qkv2` / `quant_do_delta`
+(delta_matching/sm100/quant.py:278-341).  Conventions kept from the reference: outputs are allocated by the op with
+torch's allocator and returned, the call runs on the tensors' device and that device's current stream, and misuse
+raises RuntimeError before any launch.  Layout here: codes (B, H, N, D) float8_e4m3fn, scales (B, H, N // 32) fp32.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+import torch
+
+from . import _lib
+
+E4M3 = torch.float8_e4m3fn
+BLK = 32                                  # tokens per quantisation scale
+_STATUS = {}                              # device index -> int32 status word the kernels set on a bounded-wait timeout
+_DEBUG = os.environ.get("DM_DEBUG", "0") not in ("", "0")
+
+STATUS_TEXT = {1: "TMA producer gave up waiting for a free stage", 2: "MMA issuer gave up waiting",
+               3: "compute warps gave up waiting for an accumulator", 4: "probe kernel gave up waiting"}
+
+
+def _ptr(t):
+    return ctypes.c_void_p(t.data_ptr()) if t is not None else ctypes.c_void_p(0)
+
+
+def _stream(t):
+    return ctypes.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
+
+
+def _require(cond, msg):
+    if not cond:
+        raise RuntimeError("delta_matching: " + msg)
+
+
+def _cuda(*ts):
+    dev = None
+    for t in ts:
+        if t is None:
+            continue
+        _require(isinstance(t, torch.Tensor) and t.is_cuda, "every tensor must be a CUDA tensor")
+        _require(t.numel() > 0, "empty tensor")
+        dev = dev or t.device
+        _require(t.device == dev, "every tensor must be on the same device")
+    return dev
+
+
+def status_word(device) -> torch.Tensor:
+    """The per-device int32 word the kernels set when a bounded wait runs out (0 = no problem)."""
+    idx = torch.device(device).index
+    if idx is None:
+        idx = torch.cuda.current_device()
+    w = _STATUS.get(idx)
+    if w is None:
+        w = _STATUS[idx] = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", idx))
+    return w
+
+
+def check_status(device=None) -> None:
+    """Synchronise and raise RuntimeError if a kernel on `device` reported a timed-out wait since the last check."""
+    devs = [torch.device(device).index] if device is not None else list(_STATUS)
+    for idx in devs:
+        if idx is None or idx not in _STATUS:
+            continue
+        v = int(_STATUS[idx].item())
+        if v != 0:
+            _STATUS[idx].zero_()
+            raise RuntimeError(f"delta_matching: a kernel on cuda:{idx} reported status {v} "
+                               f"({STATUS_TEXT.get(v, 'unknown')}); its outputs are invalid")
+
+
+def _after(device):
+    if _DEBUG and not torch.cuda.is_current_stream_capturing():
+        check_status(device)
+
+
+def _rows(x):
+    """(B, H, N, D) bf16 view with a unit stride on D and 16-byte aligned rows (copied otherwise)."""
+    if x.stride(-1) != 1 or any(s % 8 for s in x.stride()[:-1]) or x.data_ptr() % 16:
+        x = x.contiguous()
+    return x
+
+
+# ------------------------------------------------------------------------------------------------------------ producers
+def kmean(k: torch.Tensor) -> torch.Tensor:
+    """k (B, Hk, N, D) bf16 -> (B, Hk, D) fp32 mean over tokens (fixed summation order)."""
+    dev = _cuda(k)
+    _require(k.dim() == 4 and k.dtype == torch.bfloat16, "k must be a 4-D bfloat16 tensor")
+    k = _rows(k)
+    B, Hk, N, D = k.shape
+    L = _lib.lib()
+    with torch.cuda.device(dev):
+        mean = torch.empty(B, Hk, D, device=dev, dtype=torch.float32)
+        ws = torch.empty(max(1, L.dm_quant_qkv_workspace_bytes(B, N, Hk, D)), device=dev, dtype=torch.uint8)
+        _lib.check(L.dm_kmean(_ptr(k), k.stride(0), k.stride(1), k.stride(2), B, N, Hk, D, _ptr(mean), _ptr(ws), _stream(k)))
+    return mean
+
+
+def quant_rows(x: torch.Tensor, prescale: float = 1.0, mean: torch.Tensor | None = None, o: torch.Tensor | None = None):
+    """x (B, H, N, D) bf16 -> (codes (B, H, N, D) e4m3, scales (B, H, N // 32) fp32[, delta (B, H, N) fp32 if o given]).
+    y = (x - mean[b, h]) * prescale is quantised; delta = sum_d x * o on the raw values."""
+    dev = _cuda(x, mean, o)
+    _require(x.dim() == 4 and x.dtype == torch.bfloat16, "input must be a 4-D bfloat16 tensor")
+    x = _rows(x)
+    B, H, N, D = x.shape
+    L = _lib.lib()
+    with torch.cuda.device(dev):
+        codes = torch.empty(B, H, N, D, device=dev, dtype=E4M3)
+        scales = torch.empty(B, H, N // BLK, device=dev, dtype=torch.float32)
+        delta = None
+        os_ = (0, 0, 0)
+        if o is not None:
+            _require(o.shape == x.shape and o.dtype == torch.bfloat16, "o must match dO (bfloat16, same shape)")
+            o = _rows(o)
+            os_ = (o.stride(0), o.stride(1), o.stride(2))
+            delta = torch.empty(B, H, N, device=dev, dtype=torch.float32)
+        if mean is not None:
+            _require(mean.dtype == torch.float32 and tuple(mean.shape) == (B, H, D), "mean must be fp32 (B, H, D)")
+            mean = mean.contiguous()
+        _lib.check(L.dm_quant_rows(_ptr(x), x.stride(0), x.stride(1), x.stride(2), _ptr(mean), float(prescale),
+                                   _ptr(o), *os_, B, N, H, D, _ptr(codes), _ptr(scales), _ptr(delta), _stream(x)))
+    return (codes, scales, delta) if o is not None else (codes, scales)
+
+
+def quant_qkv(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor):
+    """q (B, H, N, D), k / v (B, Hk, N, D) bf16 -> (q8, qs, k8, ks, v8, vs, kmean).  q is scaled by D^-0.5, k is centred
+    by its per-(batch, kv head) mean over tokens (returned as kmean (B, Hk, D) fp32)."""
+    dev = _cuda(q, k, v)
+    for t in (q, k, v):
+        _require(t.dim() == 4 and t.dtype == torch.bfloat16, "q, k, v must be 4-D bfloat16 tensors")
+    q, k, v = _rows(q), _rows(k), _rows(v)
+    B, H, N, D = q.shape
+    Hk = k.shape[1]
+    L = _lib.lib()
+    with torch.cuda.device(dev):
+        e = lambda h: torch.empty(B, h, N, D, device=dev, dtype=E4M3)
+        s = lambda h: torch.empty(B, h, N // BLK, device=dev, dtype=torch.float32)
+        q8, k8, v8, qs, ks, vs = e(H), e(Hk), e(Hk), s(H), s(Hk), s(Hk)
+        km = torch.empty(B, Hk, D, device=dev, dtype=torch.float32)
+        ws = torch.empty(max(1, L.dm_quant_qkv_workspace_bytes(B, N, Hk, D)), device=dev, dtype=torch.uint8)
+        _lib.check(L.dm_quant_qkv(_ptr(q), q.stride(0), q.stride(1), q.stride(2),
+                                  _ptr(k), k.stride(0), k.stride(1), k.stride(2),
+                                  _ptr(v), v.stride(0), v.stride(1), v.stride(2),
+                                  B, N, H, Hk, D, _ptr(q8), _ptr(k8), _ptr(v8), _ptr(qs), _ptr(ks), _ptr(vs), _ptr(km),
+                                  _ptr(ws), _stream(q)))
+    return q8, qs, k8, ks, v8, vs, km
+
+
+def quant_do(do: torch.Tensor, o: torch.Tensor | None = None):
+    """dO (B, H, N, D) bf16 [+ O, same logical shape] -> (dO8, dOs, delta | None); delta = rowsum(dO * O) (stale mode)."""
+    if o is None:
+        c, s = quant_rows(do)
+        return c, s, None
+    return quant_rows(do, 1.0, None, o)
+
+
+# ------------------------------------------------------------------------------------------------------------ kernels
+def _check_codes(B, H, Hk, N, D, q8, k8, v8, qs, ks, vs, do8=None, dos=None):
+    for name, t, h in (("q8", q8, H), ("k8", k8, Hk), ("v8", v8, Hk), ("do8", do8, H)):
+        if t is None:
+            continue
+        _require(t.dtype == E4M3, f"{name} must be float8_e4m3fn (e4m3 codes)")
+        _require(tuple(t.shape) == (B, h, N, D) and t.is_contiguous(), f"{name} must be contiguous (B, H, N, D)")
+    for name, t, h in (("q scales", qs, H), ("k scales", ks, Hk), ("v scales", vs, Hk), ("dO scales", dos, H)):
+        if t is None:
+            continue
+        _require(t.dtype == torch.float32, f"{name} must be fp32")
+        _require(tuple(t.shape) == (B, h, N // BLK) and t.is_contiguous(), f"{name} must be contiguous (B, H, N // 32)")
+
+
+def fwd_fp8(q8, k8, v8, qs, ks, vs, causal: bool):
+    """-> (O (B, N, H, D) bf16 contiguous, LSE (B, H, N) fp32 natural log).  Replaces the fwd_fp8 op."""
+    dev = _cuda(q8, k8, v8, qs, ks, vs)
+    _require(q8.dim() == 4 and k8.dim() == 4, "codes must be 4-D")
+    B, H, N, D = q8.shape
+    Hk = k8.shape[1]
+    _check_codes(B, H, Hk, N, D, q8, k8, v8, qs, ks, vs)
+    L = _lib.lib()
+    with torch.cuda.device(dev):
+        o = torch.empty(B, N, H, D, device=dev, dtype=torch.bfloat16)
+        lse = torch.empty(B, H, N, device=dev, dtype=torch.float32)
+        _lib.check(L.dm_fwd(_ptr(q8), _ptr(k8), _ptr(v8), _ptr(qs), _ptr(ks), _ptr(vs), B, N, H, Hk, D, int(bool(causal)),
+                            _ptr(o), o.stride(0), o.stride(1), o.stride(2), _ptr(lse), _ptr(status_word(dev)), _stream(q8)))
+        _after(dev)
+    return o, lse
+
+
+def delta_fp8(q8, k8, v8, do8, qs, ks, vs, dos, lse, causal: bool):
+    """-> matched delta (B, H, N) fp32 from pass 0 of the backward.  Replaces the delta_fp8 op."""
+    dev = _cuda(q8, k8, v8, do8, qs, ks, vs, dos, lse)
+    B, H, N, D = q8.shape
+    Hk = k8.shape[1]
+    _check_codes(B, H, Hk, N, D, q8, k8, v8, qs, ks, vs, do8, dos)
+    _require(lse.dtype == torch.float32 and tuple(lse.shape) == (B, H, N) and lse.is_contiguous(), "lse must be fp32 (B, H, N)")
+    L = _lib.lib()
+    with torch.cuda.device(dev):
+        delta = torch.empty(B, H, N, device=dev, dtype=torch.float32)
+        _lib.check(L.dm_delta(_ptr(q8), _ptr(k8), _ptr(v8), _ptr(do8), _ptr(qs), _ptr(ks), _ptr(vs), _ptr(dos), _ptr(lse),
+                              B, N, H, Hk, D, int(bool(causal)), _ptr(delta), _ptr(status_word(dev)), _stream(q8)))
+        _after(dev)
+    return delta
+
+
+def bwd_fp8(q8, k8, v8, do8, qs, ks, vs, dos, lse, delta, causal: bool, identity: bool = False):
+    """-> (dq (B, N, H, D), dk (B, N, Hk, D), dv (B, N, Hk, D)) bf16; dk / dv are already reduced over the GQA group.
+    identity=True also returns (rowsum_dS, sum_abs_PdP), fp32 (B, H, N), accumulated in the kernel before dS is
+    quantised.  Replaces the bwd_fp8_t op and the group fold of delta_matching/attn.py:114-117."""
+    dev = _cuda(q8, k8, v8, do8, qs, ks, vs, dos, lse, delta)
+    B, H, N, D = q8.shape
+    Hk = k8.shape[1]
+    _check_codes(B, H, Hk, N, D, q8, k8, v8, qs, ks, vs, do8, dos)
+    for name, t in (("lse", lse), ("delta", delta)):
+        _require(t.dtype == torch.float32 and tuple(t.shape) == (B, H, N) and t.is_contiguous(), f"{name} must be fp32 (B, H, N)")
+    L = _lib.lib()
+    with torch.cuda.device(dev):
+        dq = torch.empty(B, N, H, D, device=dev, dtype=torch.bfloat16)
+        dk = torch.empty(B, N, Hk, D, device=dev, dtype=torch.bfloat16)
+        dv = torch.empty(B, N, Hk, D, device=dev, dtype=torch.bfloat16)
+        rs = torch.empty(B, H, N, device=dev, dtype=torch.float32) if identity else None
+        ap = torch.empty(B, H, N, device=dev, dtype=torch.float32) if identity else None
+        _lib.check(L.dm_bwd(_ptr(q8), _ptr(k8), _ptr(v8), _ptr(do8), _ptr(qs), _ptr(ks), _ptr(vs), _ptr(dos),
+                            _ptr(lse), _ptr(delta), B, N, H, Hk, D, int(bool(causal)),
+                            _ptr(dq), dq.stride(0), dq.stride(1), dq.stride(2),
+                            _ptr(dk), dk.stride(0), dk.stride(1), dk.stride(2),
+                            _ptr(dv), dv.stride(0), dv.stride(1), dv.stride(2),
+                            _ptr(rs), _ptr(ap), _ptr(status_word(dev)), _stream(q8)))
+        _after(dev)
+    return (dq, dk, dv, rs, ap) if identity else (dq, dk, dv)
+
+
+def mma_tile(a, b, sfa=None, sfb=None, a_tmem=False, a_mn=False, b_mn=False, nk=4):
+    """One 128 x 128 x (32 nk) tile product through the kernels' operand paths (see dm_dbg_mma_tile); a, b uint8 /
+    e4m3 (128, 128); sfa / sfb int32 (128, 4) scale words select the block-scaled instruction."""
+    dev = _cuda(a, b, sfa, sfb)
+    L = _lib.lib()
+    with torch.cuda.device(dev):
+        out = torch.empty(128, 128, device=dev, dtype=torch.float32)
+        _lib.check(L.dm_dbg_mma_tile(_ptr(a), _ptr(b), _ptr(sfa), _ptr(sfb), int(a_tmem), int(a_mn), int(b_mn),
+                                     int(sfa is not None), int(nk), _ptr(out), _ptr(status_word(dev)), _stream(a)))
+    return out
