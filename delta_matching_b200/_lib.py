@@ -35,6 +35,8 @@ SIGNATURES = {
     "dm_delta": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _P, _P]),
     "dm_bwd": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I,
                     _P, _L, _L, _L, _P, _L, _L, _L, _P, _L, _L, _L, _P, _P, _P, _P]),
+    "dm_bwd_parts": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I,
+                          _P, _L, _L, _L, _P, _L, _L, _L, _P, _L, _L, _L, _P, _P, _I, _P, _P]),
     "dm_dbg_mma_tile": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P, _P]),
 }
 

@@ -234,14 +234,15 @@ int dm_delta(const void* q8, const void* k8, const void* v8, const void* do8,
   return e == cudaSuccess ? 0 : cuda_fail(e, "matched-delta launch");
 }
 
-int dm_bwd(const void* q8, const void* k8, const void* v8, const void* do8,
-           const float* qs, const float* ks, const float* vs, const float* dos,
-           const float* lse, const float* delta,
-           int B, int N, int H, int Hk, int D, int causal,
-           void* dq, int64_t dq_sb, int64_t dq_sn, int64_t dq_sh,
-           void* dk, int64_t dk_sb, int64_t dk_sn, int64_t dk_sh,
-           void* dv, int64_t dv_sb, int64_t dv_sn, int64_t dv_sh,
-           float* rowsum_ds, float* sum_abs_pdp, int* status, void* stream) {
+int dm_bwd_parts(const void* q8, const void* k8, const void* v8, const void* do8,
+                 const float* qs, const float* ks, const float* vs, const float* dos,
+                 const float* lse, const float* delta,
+                 int B, int N, int H, int Hk, int D, int causal,
+                 void* dq, int64_t dq_sb, int64_t dq_sn, int64_t dq_sh,
+                 void* dk, int64_t dk_sb, int64_t dk_sn, int64_t dk_sh,
+                 void* dv, int64_t dv_sb, int64_t dv_sn, int64_t dv_sh,
+                 float* rowsum_ds, float* sum_abs_pdp, int parts, int* status, void* stream) {
+  if ((parts & 3) == 0 || (parts & ~3)) return fail(DM_ERR_ARG, "delta_matching: parts must be 1 (dK/dV), 2 (dQ) or 3 (got %d)", parts);
   DM_TRY(check_shape(B, N, H, Hk, D));
   DM_TRY(check_sm100());
   DM_TRY(check_device_ptr(q8, "q8")); DM_TRY(check_device_ptr(k8, "k8")); DM_TRY(check_device_ptr(v8, "v8"));
@@ -267,10 +268,27 @@ int dm_bwd(const void* q8, const void* k8, const void* v8, const void* do8,
   p.rowsum_ds = rowsum_ds; p.sum_abs_pdp = sum_abs_pdp;
   p.sm_scale = static_cast<float>(1.0 / sqrt(static_cast<double>(D)));
   p.B = B; p.H = H; p.Hk = Hk; p.N = N; p.causal = causal ? 1 : 0; p.status = status;
-  cudaError_t e = dm::launch_bwd_dkdv(D, tq, tk, tv, td, p, static_cast<cudaStream_t>(stream));
-  if (e != cudaSuccess) return cuda_fail(e, "backward dK/dV launch");
-  e = dm::launch_bwd_dq(D, tq, tk, tv, td, p, static_cast<cudaStream_t>(stream));
-  return e == cudaSuccess ? 0 : cuda_fail(e, "backward dQ launch");
+  if (parts & 1) {
+    cudaError_t e = dm::launch_bwd_dkdv(D, tq, tk, tv, td, p, static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return cuda_fail(e, "backward dK/dV launch");
+  }
+  if (parts & 2) {
+    cudaError_t e = dm::launch_bwd_dq(D, tq, tk, tv, td, p, static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return cuda_fail(e, "backward dQ launch");
+  }
+  return 0;
+}
+
+int dm_bwd(const void* q8, const void* k8, const void* v8, const void* do8,
+           const float* qs, const float* ks, const float* vs, const float* dos,
+           const float* lse, const float* delta,
+           int B, int N, int H, int Hk, int D, int causal,
+           void* dq, int64_t dq_sb, int64_t dq_sn, int64_t dq_sh,
+           void* dk, int64_t dk_sb, int64_t dk_sn, int64_t dk_sh,
+           void* dv, int64_t dv_sb, int64_t dv_sn, int64_t dv_sh,
+           float* rowsum_ds, float* sum_abs_pdp, int* status, void* stream) {
+  return dm_bwd_parts(q8, k8, v8, do8, qs, ks, vs, dos, lse, delta, B, N, H, Hk, D, causal, dq, dq_sb, dq_sn, dq_sh,
+                      dk, dk_sb, dk_sn, dk_sh, dv, dv_sb, dv_sn, dv_sh, rowsum_ds, sum_abs_pdp, 3, status, stream);
 }
 
 int dm_dbg_mma_tile(const void* a, const void* b, const uint32_t* sfa, const uint32_t* sfb, int a_tmem, int a_mn,

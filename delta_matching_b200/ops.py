@@ -205,10 +205,11 @@ def delta_fp8(q8, k8, v8, do8, qs, ks, vs, dos, lse, causal: bool):
     return delta
 
 
-def bwd_fp8(q8, k8, v8, do8, qs, ks, vs, dos, lse, delta, causal: bool, identity: bool = False):
+def bwd_fp8(q8, k8, v8, do8, qs, ks, vs, dos, lse, delta, causal: bool, identity: bool = False, parts: int = 3):
     """-> (dq (B, N, H, D), dk (B, N, Hk, D), dv (B, N, Hk, D)) bf16; dk / dv are already reduced over the GQA group.
     identity=True also returns (rowsum_dS, sum_abs_PdP), fp32 (B, H, N), accumulated in the kernel before dS is
-    quantised.  Replaces the bwd_fp8_t op and the group fold of delta_matching/attn.py:114-117."""
+    quantised.  parts: 1 = only the dK / dV kernel, 2 = only the dQ kernel, 3 = both (the outputs of a kernel that did
+    not run are uninitialised).  Replaces the bwd_fp8_t op and the group fold of delta_matching/attn.py:114-117."""
     dev = _cuda(q8, k8, v8, do8, qs, ks, vs, dos, lse, delta)
     B, H, N, D = q8.shape
     Hk = k8.shape[1]
@@ -222,12 +223,12 @@ def bwd_fp8(q8, k8, v8, do8, qs, ks, vs, dos, lse, delta, causal: bool, identity
         dv = torch.empty(B, N, Hk, D, device=dev, dtype=torch.bfloat16)
         rs = torch.empty(B, H, N, device=dev, dtype=torch.float32) if identity else None
         ap = torch.empty(B, H, N, device=dev, dtype=torch.float32) if identity else None
-        _lib.check(L.dm_bwd(_ptr(q8), _ptr(k8), _ptr(v8), _ptr(do8), _ptr(qs), _ptr(ks), _ptr(vs), _ptr(dos),
+        _lib.check(L.dm_bwd_parts(_ptr(q8), _ptr(k8), _ptr(v8), _ptr(do8), _ptr(qs), _ptr(ks), _ptr(vs), _ptr(dos),
                             _ptr(lse), _ptr(delta), B, N, H, Hk, D, int(bool(causal)),
                             _ptr(dq), dq.stride(0), dq.stride(1), dq.stride(2),
                             _ptr(dk), dk.stride(0), dk.stride(1), dk.stride(2),
                             _ptr(dv), dv.stride(0), dv.stride(1), dv.stride(2),
-                            _ptr(rs), _ptr(ap), _ptr(status_word(dev)), _stream(q8)))
+                            _ptr(rs), _ptr(ap), int(parts), _ptr(status_word(dev)), _stream(q8)))
         _after(dev)
     return (dq, dk, dv, rs, ap) if identity else (dq, dk, dv)
 

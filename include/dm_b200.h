@@ -101,6 +101,18 @@ int dm_bwd(const void* q8, const void* k8, const void* v8, const void* do8,
            void* dv, int64_t dv_sb, int64_t dv_sn, int64_t dv_sh,
            float* rowsum_ds, float* sum_abs_pdp, int* status, void* stream);
 
+/* dm_bwd with a choice of kernels: parts = 1 runs only the dK / dV kernel, 2 only the dQ kernel, 3 both (what dm_bwd
+ * does).  The reference launches its pass 1 and pass 2 from one op (csrc/flash_bwd_fp8v10_launch.h:158-163); the split
+ * exists so that each kernel can be timed and profiled alone. */
+int dm_bwd_parts(const void* q8, const void* k8, const void* v8, const void* do8,
+                 const float* qs, const float* ks, const float* vs, const float* dos,
+                 const float* lse, const float* delta,
+                 int B, int N, int H, int Hk, int D, int causal,
+                 void* dq, int64_t dq_sb, int64_t dq_sn, int64_t dq_sh,
+                 void* dk, int64_t dk_sb, int64_t dk_sn, int64_t dk_sh,
+                 void* dv, int64_t dv_sb, int64_t dv_sn, int64_t dv_sh,
+                 float* rowsum_ds, float* sum_abs_pdp, int parts, int* status, void* stream);
+
 /* One 128 x 128 x (32 * nk) e4m3 tile product through the operand paths the kernels use (unit-test hook; the
  * reference has per-kernel debug ops instead, csrc/delta_matching_api.cpp:611-661).  a, b: 128 x 128 e4m3 row-major
  * device buffers; sfa / sfb: 128 x 4 uint32 scale words (block-scaled runs only); out: 128 x 128 fp32. */
