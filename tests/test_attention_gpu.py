@@ -54,7 +54,29 @@ def test_matches_emulation(B, N, H, Hk, causal, mode, oracle):
     assert not fails, "; ".join(fails)
 
 
-@pytest.mark.parametrize("case", ["c1_matched", "c1_stale", "gqa_noncausal_stale"])
+@pytest.mark.parametrize("mode", ["matched", "stale"])
+@pytest.mark.parametrize("B,N,H,Hk,causal", [(1, 128, 2, 2, True), (1, 384, 4, 2, True), (1, 256, 2, 1, False),
+                                             (1, 1024, 2, 1, True)])
+def test_matches_emulation_hd256(B, N, H, Hk, causal, mode, oracle):
+    """head_dim 256 (the reference's gates for its hd256 kernels: tests/test_sm100_hd256.py:97, 122-147)."""
+    if mode == "matched" and not causal:
+        pytest.skip("matched needs causal")
+    q, k, v, do = oracle.make_inputs(B, N, H, Hk, 256, seed=7, device="cuda")
+    got = run_ops(q, k, v, do, causal, mode)
+    em = oracle.dm_oracle(q, k, v, do, causal, mode, k_mean=got["kmean"], o_for_stale=got["O"] if mode == "stale" else None)
+    ex = oracle.attention_exact(q, k, v, do, causal)
+    case = f"hd256_{B}_{N}_{H}_{Hk}_{int(causal)}_{mode}"
+    assert (got["LSE"] - em["LSE"]).abs().max().item() <= 1e-4 + 1e-5 * em["LSE"].abs().max().item(), "LSE"
+    for nm in NAMES:
+        e_c, e_e = oracle.rel_l2(got[nm], ex[nm]), oracle.rel_l2(em[nm], ex[nm])
+        dist = oracle.rel_l2(got[nm], em[nm])
+        record("emu", case, nm, dist)
+        assert e_c <= 1.01 * e_e + 1e-5, f"{nm}: err vs exact {e_c:.3e}, emulation {e_e:.3e}"
+        assert dist <= EMU_DIST[nm], f"{nm}: dist to emulation {dist:.3e}"
+        assert e_c < TOL_EXACT[nm], nm
+
+
+@pytest.mark.parametrize("case", ["c1_matched", "c1_stale", "gqa_noncausal_stale", "hd256_matched"])
 def test_golden_vectors(case, oracle):
     """Against the committed outputs of the reference's own emulation (generated with its default K mean)."""
     g = load_golden(case)
