@@ -119,6 +119,20 @@ int dm_bwd_parts(const void* q8, const void* k8, const void* v8, const void* do8
 int dm_dbg_mma_tile(const void* a, const void* b, const uint32_t* sfa, const uint32_t* sfb, int a_tmem, int a_mn,
                     int b_mn, int scaled, int nk, float* out, int* status, void* stream);
 
+/* K mean without a workspace argument, for callers that cannot allocate device memory themselves (code inside a
+ * no-allocation region of its host framework, or a plugin that owns no memory pool): same inputs, same kernels and
+ * bit-identical result as dm_kmean, but the chunk-sum scratch is an array built into the library (4 MiB on every GPU
+ * that loads it, held until the process exits).  This entry point has no counterpart in the reference.
+ *   - Limit: B * Hk * (N / 64) * D <= 1048576; larger problems are refused with a message (use dm_kmean).
+ *   - The first call on each device looks up the array's device address; make that call before any stream capture.
+ *   - It calls no allocation routine of any kind and does not synchronise.
+ *   - All calls on a device share the one array, which keeps the previous call's contents (nothing needs clearing:
+ *     every value read is written first by the same call); two calls that overlap on the GPU race on it, so issue them
+ *     on one stream or order them yourself.
+ * Returns 0, or a negative code with a message in err (may be NULL). */
+int dm_kmean_static(const void* k, int64_t k_sb, int64_t k_sh, int64_t k_sn, int B, int N, int Hk, int D, float* mean,
+                    void* stream, char* err, int err_len);
+
 #ifdef __cplusplus
 }
 #endif
