@@ -4,7 +4,8 @@
 // Arithmetic shared with the backward (delta_matching/sm100/attention_math_sm100.py:26-45; emulation
 // delta_matching/reference.py:483, 491, 526-535):
 //   c = (ks_b * qs) * log2e;  l2 = lse * log2e;  P = ex2(fma(S_acc, c, -l2));  a = vs_b * dos;  dP = dP_acc * a.
-// Sums: fp32 FMA chains of 16 elements, folded into fp64 per row; one fp64 divide and one fp32 store per row.
+// Sums: four fp32 FMA chains of 8 elements per 32-key block, folded into fp64 per row (the power-of-two factor a is
+// applied once per block, which is exact); one fp64 divide and one fp32 store per row.
 //
 // CTA = one 128-query tile of one (batch, query head); S = Q8 K8^T and dP = dO8 V8^T on tcgen05 (kind::f8f6f4) into
 // two 128-column TMEM accumulators.  Warps 0-3 compute (thread t = TMEM lane t = query row t), warp 4 TMA, warp 5 MMA.
@@ -138,37 +139,55 @@ delta_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ C
     const float neg_l2 = -(p.lse[static_cast<size_t>(bh) * p.N + row] * kLog2e);
     double num = 0.0, den = 0.0;
     bool ok = true;
+    const float* ks_base = p.ks + static_cast<size_t>(bhk) * nblk;
+    const float* vs_base = p.vs + static_cast<size_t>(bhk) * nblk;
+    float4 ks4 = *reinterpret_cast<const float4*>(ks_base);
+    float4 vs4 = *reinterpret_cast<const float4*>(vs_base);
+    const float2 nl2 = splat2(neg_l2);
     for (int it = 0; it < n_it; ++it) {
-      const float4 ks4 = *reinterpret_cast<const float4*>(p.ks + static_cast<size_t>(bhk) * nblk + it * 4);
-      const float4 vs4 = *reinterpret_cast<const float4*>(p.vs + static_cast<size_t>(bhk) * nblk + it * 4);
       const float cb[4] = {(ks4.x * qs) * kLog2e, (ks4.y * qs) * kLog2e, (ks4.z * qs) * kLog2e, (ks4.w * qs) * kLog2e};
-      const float ab[4] = {vs4.x * dos, vs4.y * dos, vs4.z * dos, vs4.w * dos};
+      // a = vs * dos is a power of two, so P * (dP_acc * a) == (P * dP_acc) * a exactly: a is applied once per block
+      const double ab[4] = {static_cast<double>(vs4.x * dos), static_cast<double>(vs4.y * dos),
+                            static_cast<double>(vs4.z * dos), static_cast<double>(vs4.w * dos)};
+      if (it + 1 < n_it) {
+        ks4 = *reinterpret_cast<const float4*>(ks_base + (it + 1) * 4);
+        vs4 = *reinterpret_cast<const float4*>(vs_base + (it + 1) * 4);
+      }
       const bool diag = p.causal && (it == qt);
       if (!(ok = wait_warp(bar_s, it & 1, abort_flag))) break;
       tc_fence_after();
+      uint32_t rs[2][32], rd[2][32];
+      tmem_ld32(tmem + lane_base + C::kColS, rs[0]);
+      tmem_ld32(tmem + lane_base + C::kColDp, rd[0]);
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
-        uint32_t rs[32], rd[32];
-        tmem_ld32(tmem + lane_base + C::kColS + 32 * c, rs);
-        tmem_ld32(tmem + lane_base + C::kColDp + 32 * c, rd);
         tmem_wait_ld();
-        float n0 = 0.f, n1 = 0.f, d0 = 0.f, d1 = 0.f;
-#pragma unroll
-        for (int e = 0; e < 16; ++e) {
-          float s0 = __uint_as_float(rs[e]), s1 = __uint_as_float(rs[16 + e]);
-          if (diag && (32 * c + e > tid)) s0 = -INFINITY;
-          if (diag && (32 * c + 16 + e > tid)) s1 = -INFINITY;
-          const float p0 = ex2_approx(fmaf(s0, cb[c], neg_l2));
-          const float p1 = ex2_approx(fmaf(s1, cb[c], neg_l2));
-          n0 = fmaf(p0, __uint_as_float(rd[e]) * ab[c], n0);
-          n1 = fmaf(p1, __uint_as_float(rd[16 + e]) * ab[c], n1);
-          d0 += p0;
-          d1 += p1;
+        if (c < 3) {
+          tmem_ld32(tmem + lane_base + C::kColS + 32 * (c + 1), rs[(c + 1) & 1]);
+          tmem_ld32(tmem + lane_base + C::kColDp + 32 * (c + 1), rd[(c + 1) & 1]);
         }
-        num += static_cast<double>(n0);
-        num += static_cast<double>(n1);
-        den += static_cast<double>(d0);
-        den += static_cast<double>(d1);
+        uint32_t(&s)[32] = rs[c & 1];
+        const uint32_t(&dp)[32] = rd[c & 1];
+        if (diag) {
+#pragma unroll
+          for (int e = 0; e < 32; ++e)
+            if (32 * c + e > tid) s[e] = 0xff800000u;
+        }
+        const float2 c2 = splat2(cb[c]);
+        float2 n0 = make_float2(0.f, 0.f), n1 = n0, d0 = n0, d1 = n0;
+#pragma unroll
+        for (int e = 0; e < 16; e += 2) {
+          const float2 p0 = ex2_2(fma2(make_float2(__uint_as_float(s[2 * e]), __uint_as_float(s[2 * e + 1])), c2, nl2));
+          const float2 p1 = ex2_2(fma2(make_float2(__uint_as_float(s[2 * e + 2]), __uint_as_float(s[2 * e + 3])), c2, nl2));
+          n0 = fma2(p0, make_float2(__uint_as_float(dp[2 * e]), __uint_as_float(dp[2 * e + 1])), n0);
+          n1 = fma2(p1, make_float2(__uint_as_float(dp[2 * e + 2]), __uint_as_float(dp[2 * e + 3])), n1);
+          d0 = add2(d0, p0);
+          d1 = add2(d1, p1);
+        }
+        num += (static_cast<double>(n0.x) + static_cast<double>(n0.y) + static_cast<double>(n1.x) +
+                static_cast<double>(n1.y)) * ab[c];
+        den += static_cast<double>(d0.x) + static_cast<double>(d0.y) + static_cast<double>(d1.x) +
+               static_cast<double>(d1.y);
       }
       tc_fence_before();
       mbar_arrive(bar_c);

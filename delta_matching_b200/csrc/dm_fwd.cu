@@ -161,45 +161,52 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
     const float qsl = p.qs[static_cast<size_t>(bh) * nblk + row / 32] * kLog2e;
     float m = 0.f, l = 0.f;
     bool ok = true;
+    const float* ks_base = p.ks + static_cast<size_t>(bhk) * nblk;
+    const float* vs_base = p.vs + static_cast<size_t>(bhk) * nblk;
+    float4 ks4 = *reinterpret_cast<const float4*>(ks_base + kt_first * 4);
+    float4 vs4 = *reinterpret_cast<const float4*>(vs_base + kt_first * 4);
     for (int it = 0; it < n_it; ++it) {
       const int kt = kt_first - it;
-      const float4 ks4 = *reinterpret_cast<const float4*>(p.ks + static_cast<size_t>(bhk) * nblk + kt * 4);
-      const float4 vs4 = *reinterpret_cast<const float4*>(p.vs + static_cast<size_t>(bhk) * nblk + kt * 4);
       const float cb[4] = {qsl * ks4.x, qsl * ks4.y, qsl * ks4.z, qsl * ks4.w};
       const uint32_t sfb = pack4(scale_to_sb(vs4.x), scale_to_sb(vs4.y), scale_to_sb(vs4.z), scale_to_sb(vs4.w));
+      if (it + 1 < n_it) {                     // scales of the next key tile: in flight while this tile is processed
+        ks4 = *reinterpret_cast<const float4*>(ks_base + (kt - 1) * 4);
+        vs4 = *reinterpret_cast<const float4*>(vs_base + (kt - 1) * 4);
+      }
       const bool diag = p.causal && (kt == qt);
       if (!(ok = wait_warp(bar_s, it & 1, abort_flag))) break;
       tc_fence_after();
       float bsum[4], kb[4], bmax[4];
+      uint32_t r[2][32];
+      tmem_ld32(tmem + lane_base + C::kColS, r[0]);
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld32(tmem + lane_base + C::kColS + 32 * c, r);
         tmem_wait_ld();
-        float s[32];
+        if (c < 3) tmem_ld32(tmem + lane_base + C::kColS + 32 * (c + 1), r[(c + 1) & 1]);   // next chunk in flight
+        uint32_t(&rc)[32] = r[c & 1];
+        if (diag) {
 #pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          s[e] = __uint_as_float(r[e]);
-          if (diag && (32 * c + e > tid)) s[e] = -INFINITY;
+          for (int e = 0; e < 32; ++e)
+            if (32 * c + e > tid) rc[e] = 0xff800000u;       // -inf: key index above the query index
         }
-        float mx = s[0];
+        float2 s2[16];
 #pragma unroll
-        for (int e = 1; e < 32; ++e) mx = fmaxf(mx, s[e]);
-        bmax[c] = mx * cb[c];
+        for (int e = 0; e < 16; ++e) s2[e] = make_float2(__uint_as_float(rc[2 * e]), __uint_as_float(rc[2 * e + 1]));
+        bmax[c] = max32(s2) * cb[c];
         kb[c] = fmaxf(floorf(bmax[c]), -1e30f);
-        const float bias = 7.0f - kb[c];
-        float sum = 0.f;
+        const float2 c2 = splat2(cb[c]), bias2 = splat2(7.0f - kb[c]);
+        float2 sum0 = make_float2(0.f, 0.f), sum1 = make_float2(0.f, 0.f);
         uint32_t codes[8];
 #pragma unroll
-        for (int e = 0; e < 32; e += 4) {
-          const float p0 = ex2_approx(fmaf(s[e + 0], cb[c], bias));
-          const float p1 = ex2_approx(fmaf(s[e + 1], cb[c], bias));
-          const float p2 = ex2_approx(fmaf(s[e + 2], cb[c], bias));
-          const float p3 = ex2_approx(fmaf(s[e + 3], cb[c], bias));
-          sum += (p0 + p1) + (p2 + p3);
-          codes[e / 4] = cvt_e4m3x4(p0, p1, p2, p3);
+        for (int e = 0; e < 16; e += 2) {
+          const float2 p0 = ex2_2(fma2(s2[e], c2, bias2));
+          const float2 p1 = ex2_2(fma2(s2[e + 1], c2, bias2));
+          sum0 = add2(sum0, p0);
+          sum1 = add2(sum1, p1);
+          codes[e / 2] = cvt_e4m3x4(p0.x, p0.y, p1.x, p1.y);
         }
-        bsum[c] = sum;
+        sum0 = add2(sum0, sum1);
+        bsum[c] = sum0.x + sum0.y;
         tmem_st8(tmem + lane_base + C::kColS + 8 * c, codes);
       }
       const float mcand = ceilf(fmaxf(fmaxf(bmax[0], bmax[1]), fmaxf(bmax[2], bmax[3])));

@@ -4,6 +4,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <math_constants.h>
 
 namespace dm {
 
@@ -213,7 +214,52 @@ __device__ __forceinline__ uint32_t cvt_e4m3x2(float lo, float hi) {
   return r;
 }
 __device__ __forceinline__ uint32_t cvt_e4m3x4(float a, float b, float c, float d) {
-  return cvt_e4m3x2(a, b) | (cvt_e4m3x2(c, d) << 16);
+  uint32_t w;
+  asm("{\n\t.reg .b16 lo, hi;\n\t"
+      "cvt.rn.satfinite.e4m3x2.f32 lo, %2, %1;\n\t"
+      "cvt.rn.satfinite.e4m3x2.f32 hi, %4, %3;\n\t"
+      "mov.b32 %0, {lo, hi};\n\t}"
+      : "=r"(w)
+      : "f"(a), "f"(b), "f"(c), "f"(d));
+  return w;
+}
+
+// ------------------------------------------------------------------------------------------------ packed fp32 pairs
+// sm_100 executes fma / mul / add on two fp32 lanes per instruction (same rounding as the scalar forms), which halves
+// the issue slots of the softmax arithmetic.
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) { return __ffma2_rn(a, b, c); }
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) { return __fmul2_rn(a, b); }
+__device__ __forceinline__ float2 add2(float2 a, float2 b) { return __fadd2_rn(a, b); }
+__device__ __forceinline__ float2 splat2(float a) { return make_float2(a, a); }
+__device__ __forceinline__ float2 ex2_2(float2 x) { return make_float2(ex2_approx(x.x), ex2_approx(x.y)); }
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float m;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(m) : "f"(a), "f"(b), "f"(c));
+  return m;
+}
+// max over 32 floats held as 16 pairs (exact, order-free)
+__device__ __forceinline__ float max32(const float2 (&v)[16]) {
+  float m0 = max3(v[0].x, v[0].y, v[1].x), m1 = max3(v[1].y, v[2].x, v[2].y);
+  float m2 = max3(v[3].x, v[3].y, v[4].x), m3 = max3(v[4].y, v[5].x, v[5].y);
+#pragma unroll
+  for (int i = 6; i < 14; i += 4) {
+    m0 = max3(m0, v[i].x, v[i].y);
+    m1 = max3(m1, v[i + 1].x, v[i + 1].y);
+    m2 = max3(m2, v[i + 2].x, v[i + 2].y);
+    m3 = max3(m3, v[i + 3].x, v[i + 3].y);
+  }
+  m0 = max3(m0, v[14].x, v[14].y);
+  m1 = max3(m1, v[15].x, v[15].y);
+  return fmaxf(max3(m0, m1, m2), m3);
+}
+// 32 floats (16 pairs) times a common factor -> 8 words of four e4m3 codes
+__device__ __forceinline__ void codes32(const float2 (&v)[16], float inv, uint32_t (&w)[8]) {
+  const float2 i2 = make_float2(inv, inv);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const float2 a = mul2(v[2 * i], i2), b = mul2(v[2 * i + 1], i2);
+    w[i] = cvt_e4m3x4(a.x, a.y, b.x, b.y);
+  }
 }
 
 }  // namespace dm
