@@ -306,4 +306,21 @@ int dm_dbg_mma_tile(const void* a, const void* b, const uint32_t* sfa, const uin
   return e == cudaSuccess ? 0 : cuda_fail(e, "probe launch");
 }
 
+int dm_dbg_mma_cycles(const void* a, const void* b, int a_tmem, int a_mn, int b_mn, int scaled, int nk, int n_cols,
+                      int repeat, unsigned long long* cycles, int* status, void* stream) {
+  DM_TRY(check_sm100());
+  DM_TRY(check_device_ptr(a, "a")); DM_TRY(check_device_ptr(b, "b")); DM_TRY(check_device_ptr(cycles, "cycles"));
+  if (nk < 1 || nk > 4) return fail(DM_ERR_ARG, "delta_matching: nk must be in 1..4 (got %d)", nk);
+  if (n_cols != 64 && n_cols != 128) return fail(DM_ERR_ARG, "delta_matching: n_cols must be 64 or 128");
+  if (nk != 4) return fail(DM_ERR_ARG, "delta_matching: the timing probe issues groups of nk = 4 steps");
+  if (repeat < 1 || repeat > 4096) return fail(DM_ERR_ARG, "delta_matching: repeat must be in 1..4096");
+  if (a_tmem && a_mn) return fail(DM_ERR_ARG, "delta_matching: an A operand in TMEM has no major mode (a_mn must be 0)");
+  CUtensorMap ta, tb;
+  DM_TRY(make_code_map(&ta, a, 128, 128));
+  DM_TRY(make_code_map(&tb, b, 128, 128));
+  dm::ProbeParams p{static_cast<const uint8_t*>(a), nullptr, nullptr, nullptr, a_tmem, a_mn, b_mn, scaled, nk, status};
+  cudaError_t e = dm::launch_mma_cycles(ta, tb, p, n_cols, repeat, cycles, static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? 0 : cuda_fail(e, "probe launch");
+}
+
 }  // extern "C"

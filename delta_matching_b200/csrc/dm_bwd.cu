@@ -16,6 +16,7 @@
 //              dQ's scale along keys = ds_sb (+) ks_sb;  dQ = (dS K) * D^-0.5.
 // Both kernels evaluate P and dS with the same operations on the same accumulators, so the dS codes of kernel 2 are the
 // codes of kernel 1 whenever the two MMA orientations return the same fp32 sums.
+#include <cstdlib>
 #include <cuda_bf16.h>
 #include "dm_common.cuh"
 #include "dm_kernels.h"
@@ -151,6 +152,8 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     // ------------------------------------------------------------------------------------------ MMA issuer
     if (elect_one()) {
       constexpr uint32_t kIdesc = idesc_f8(128, 128, false, false);
+      const uint32_t k_lo = desc_lo(smem_u32(sK)), v_lo = desc_lo(smem_u32(sV));
+      const uint32_t q_lo0 = desc_lo(smem_u32(sQ)), do_lo0 = desc_lo(smem_u32(sDo));
       bool ok = wait_or_abort(bar_kv, 0, abort_flag);
       for (int it = 0; ok && it < n_it; ++it) {
         const int st = it % C::kStages;
@@ -158,19 +161,17 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         // the previous chains still read the code and scale columns that the next S^T / dP^T overwrite
         if (it > 0 && !(ok = wait_or_abort(bar_done, (it - 1) & 1, abort_flag))) break;
         tc_fence_after();
-        const uint32_t q_addr = smem_u32(sQ + st * C::kTileBytes), do_addr = smem_u32(sDo + st * C::kTileBytes);
+        const uint32_t q_lo = q_lo0 + st * (C::kTileBytes >> 4), do_lo = do_lo0 + st * (C::kTileBytes >> 4);
 #pragma unroll
         for (int ks = 0; ks < D / 32; ++ks) {
-          const uint32_t off = (ks / 4) * 16384 + (ks % 4) * 32;
-          mma_f8_ss(tmem + C::kColS, smem_desc_sw128(smem_u32(sK) + off, 16, 1024),
-                    smem_desc_sw128(q_addr + off, 16, 1024), kIdesc, ks > 0);
+          const uint32_t off = (ks / 4) * 1024 + (ks % 4) * 2;      // descriptor units of 16 bytes
+          mma_f8_ss(tmem + C::kColS, k_lo + off, q_lo + off, kIdesc, ks > 0);
         }
         if (DK) {
 #pragma unroll
           for (int ks = 0; ks < D / 32; ++ks) {
-            const uint32_t off = (ks / 4) * 16384 + (ks % 4) * 32;
-            mma_f8_ss(tmem + C::kColDp, smem_desc_sw128(smem_u32(sV) + off, 16, 1024),
-                      smem_desc_sw128(do_addr + off, 16, 1024), kIdesc, ks > 0);
+            const uint32_t off = (ks / 4) * 1024 + (ks % 4) * 2;
+            mma_f8_ss(tmem + C::kColDp, v_lo + off, do_lo + off, kIdesc, ks > 0);
           }
         }
         tc_commit(bar_s);
@@ -182,13 +183,11 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           for (int s = 0; s < C::kSub; ++s) {
             // contraction over the 128 queries of the tile: B = dO / Q tile read MN-major, 32 query rows per step
             if (DV)
-              mma_mxf8_ts(tmem + C::kColDv + s * 128, tmem + C::kColS + ks * 8,
-                          smem_desc_sw128(do_addr + s * 16384 + ks * 4096, 16, 1024),
+              mma_mxf8_ts(tmem + C::kColDv + s * 128, tmem + C::kColS + ks * 8, do_lo + s * 1024 + ks * 256,
                           idesc_mxf8(128, 128, false, true, ks, ks), tmem + C::kColSfaV, tmem + C::kColOne,
                           (it > 0) || (ks > 0));
             if (DK)
-              mma_mxf8_ts(tmem + C::kColDk + s * 128, tmem + C::kColDp + ks * 8,
-                          smem_desc_sw128(q_addr + s * 16384 + ks * 4096, 16, 1024),
+              mma_mxf8_ts(tmem + C::kColDk + s * 128, tmem + C::kColDp + ks * 8, q_lo + s * 1024 + ks * 256,
                           idesc_mxf8(128, 128, false, true, ks, ks), tmem + C::kColSfaK, tmem + C::kColOne,
                           (it > 0) || (ks > 0));
           }
@@ -325,9 +324,372 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   if (warp == 5) tmem_dealloc(tmem, C::kTmemCols);
 }
 
+// ================================================================================================ dK / dV, pipelined (D = 128)
+// One CTA per SM: G compute groups of four warps (G = 2 or 4; group g owns the query blocks [g * 4/G, (g+1) * 4/G) of
+// every tile, 32 query columns per block; thread t % 128 = key row = TMEM lane), then one TMA warp and one MMA warp.
+// TMEM: one 128-column region is time-shared by S^T and dP^T (each is pulled into registers as soon as it lands, which
+// frees the region for the other), P^T codes, dS^T codes and the scale words have columns of their own, dV and dK
+// accumulate over all (query head of the group, query tile) iterations.  The tensor pipe therefore runs dP^T(i),
+// dV(i), S^T(i+1), dK(i) behind the exponentials of tile i.
+template <int G>
+struct KvPipeCfg {
+  static constexpr int kTileBytes = 128 * 128;
+  static constexpr int kStages = 4;
+  static constexpr int kGroups = G;
+  static constexpr int kChunks = 4 / G;      // 32-column query blocks per thread and tile
+  static constexpr int kThreads = kGroups * 128 + 64;
+  static constexpr int kTmemCols = 512;
+  static constexpr int kColSd = 0;           // S^T, then dP^T (fp32)
+  static constexpr int kColPc = 128;         // P^T codes: 8 columns per query block
+  static constexpr int kColDc = 160;         // dS^T codes
+  static constexpr int kColXv = 192;         // 4 x 4 columns: dV scale word of query block b (byte 0)
+  static constexpr int kColXk = 208;         // 4 x 4 columns: dK scale word of query block b
+  static constexpr int kColOne = 224;        // 4 columns of 0x7F7F7F7F
+  static constexpr int kColDv = 256, kColDk = 384;
+  static constexpr int kSmemK = 0;
+  static constexpr int kSmemV = kTileBytes;
+  static constexpr int kSmemQ = 2 * kTileBytes;                      // [kStages]
+  static constexpr int kSmemDo = kSmemQ + kStages * kTileBytes;      // [kStages]
+  static constexpr int kSmemVec = kSmemDo + kStages * kTileBytes;    // [kStages] x (lse[128], delta[128]) floats
+  static constexpr int kSmemXch = kSmemVec + kStages * 1024;         // 2 x [16 warps] floats
+  static constexpr int kSmemBar = kSmemXch + 2 * 16 * 4;
+  static constexpr int kSmemBytes = kSmemBar + 256 + 1024;
+};
+
+template <int G>
+__global__ void __launch_bounds__(KvPipeCfg<G>::kThreads, 1)
+bwd_dkdv_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                     const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
+                     const BwdParams p) {
+  using C = KvPipeCfg<G>;
+  constexpr int kW = C::kGroups * 4;                 // compute warps; warp kW = TMA, kW + 1 = MMA
+  constexpr int CH = C::kChunks;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sK = smem + C::kSmemK;
+  uint8_t* sV = smem + C::kSmemV;
+  uint8_t* sQ = smem + C::kSmemQ;
+  uint8_t* sDo = smem + C::kSmemDo;
+  float* sVec = reinterpret_cast<float*>(smem + C::kSmemVec);
+  float* sXch = reinterpret_cast<float*>(smem + C::kSmemXch);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kSmemBar);
+  uint64_t* bar_kv = bars + 0;
+  uint64_t* bar_s = bars + 1;        // S^T landed in the shared region (MMA commit)
+  uint64_t* bar_sfree = bars + 2;    // every compute warp holds its S^T columns (one arrival per warp)
+  uint64_t* bar_dp = bars + 3;       // dP^T landed
+  uint64_t* bar_dpfree = bars + 4;   // every compute warp holds its dP^T columns
+  uint64_t* bar_pv = bars + 5;       // P^T codes + dV scale words written
+  uint64_t* bar_pk = bars + 6;       // dS^T codes + dK scale words written
+  uint64_t* bar_done = bars + 7;     // dV and dK chains of the iteration done (MMA commit)
+  uint64_t* full = bars + 8;         // [kStages] Q, dO, lse, delta of the stage landed
+  uint64_t* empty = bars + 12;       // [kStages]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 17);
+
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int n_t = p.N / 128;
+  const int kt = blockIdx.x;                          // causal: tile 0 has the most query tiles and starts first
+  const int bhk = blockIdx.y;
+  const int b = bhk / p.Hk, hk = bhk % p.Hk;
+  const int rep = p.H / p.Hk;
+  const int qt0 = p.causal ? kt : 0;
+  const int n_qi = n_t - qt0;
+  const int n_it = rep * n_qi;                        // iteration = (query head of the group, query tile)
+
+  if (tid == 0) {
+    mbar_init(bar_kv, 1);
+    mbar_init(bar_s, 1);
+    mbar_init(bar_dp, 1);
+    mbar_init(bar_done, 1);
+    mbar_init(bar_sfree, kW);
+    mbar_init(bar_dpfree, kW);
+    mbar_init(bar_pv, kW);
+    mbar_init(bar_pk, kW);
+    for (int s = 0; s < C::kStages; ++s) {
+      mbar_init(full + s, 1);
+      mbar_init(empty + s, 1);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == kW + 1) {
+    tmem_alloc(tmem_slot, C::kTmemCols);
+    tmem_relinquish();
+    tc_fence_before();
+  }
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp == kW) {
+    // ------------------------------------------------------------------------------------------ TMA producer
+    if (elect_one()) {
+      tma_prefetch_desc(&tm_q);
+      tma_prefetch_desc(&tm_k);
+      tma_prefetch_desc(&tm_v);
+      tma_prefetch_desc(&tm_do);
+      mbar_expect_tx(bar_kv, 2 * C::kTileBytes);
+      tma_load_2d(sK, &tm_k, bar_kv, 0, bhk * p.N + kt * 128);
+      tma_load_2d(sV, &tm_v, bar_kv, 0, bhk * p.N + kt * 128);
+      int h = hk * rep, qi = 0;
+      for (int it = 0; it < n_it; ++it) {
+        const int st = it % C::kStages;
+        if (it >= C::kStages) {
+          if (!wait_or_abort(empty + st, ((it / C::kStages) - 1) & 1, abort_flag)) {
+            raise_abort(abort_flag, p.status, kStatusTimeoutProducer);
+            break;
+          }
+        }
+        const size_t row = static_cast<size_t>(b * p.H + h) * p.N + (qt0 + qi) * 128;
+        mbar_expect_tx(full + st, 2 * C::kTileBytes + 1024);
+        tma_load_2d(sQ + st * C::kTileBytes, &tm_q, full + st, 0, static_cast<int>(row));
+        tma_load_2d(sDo + st * C::kTileBytes, &tm_do, full + st, 0, static_cast<int>(row));
+        bulk_load_1d(sVec + st * 256, p.lse + row, 512, full + st);
+        bulk_load_1d(sVec + st * 256 + 128, p.delta + row, 512, full + st);
+        if (++qi == n_qi) {
+          qi = 0;
+          ++h;
+        }
+      }
+    }
+  } else if (warp == kW + 1) {
+    // ------------------------------------------------------------------------------------------ MMA issuer
+    if (elect_one()) {
+      constexpr uint32_t kIdesc = idesc_f8(128, 128, false, false);
+      constexpr uint32_t kIdescBs = idesc_mxf8(128, 128, false, true, 0, 0);
+      const uint32_t k_lo = desc_lo(smem_u32(sK)), v_lo = desc_lo(smem_u32(sV));
+      const uint32_t q_lo0 = desc_lo(smem_u32(sQ)), do_lo0 = desc_lo(smem_u32(sDo));
+      bool ok = wait_or_abort(bar_kv, 0, abort_flag);
+      if (ok) ok = wait_or_abort(full + 0, 0, abort_flag);
+      if (ok) {
+        tc_fence_after();
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) mma_f8_ss(tmem + C::kColSd, k_lo + ks * 2, q_lo0 + ks * 2, kIdesc, ks > 0);
+        tc_commit(bar_s);
+      }
+      for (int it = 0; ok && it < n_it; ++it) {
+        const int st = it % C::kStages;
+        const uint32_t q_lo = q_lo0 + st * (C::kTileBytes >> 4), do_lo = do_lo0 + st * (C::kTileBytes >> 4);
+        const uint32_t ph = it & 1;
+        if (!(ok = wait_or_abort(bar_sfree, ph, abort_flag))) break;
+        tc_fence_after();
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) mma_f8_ss(tmem + C::kColSd, v_lo + ks * 2, do_lo + ks * 2, kIdesc, ks > 0);
+        tc_commit(bar_dp);
+        if (!(ok = wait_or_abort(bar_pv, ph, abort_flag))) break;
+        tc_fence_after();
+        // dV += P^T dO: A = P^T codes in TMEM (8 columns per 32-query step), B = dO tile MN-major (32 query rows per step)
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks)
+          mma_mxf8_ts(tmem + C::kColDv, tmem + C::kColPc + ks * 8, do_lo + ks * 256, kIdescBs, tmem + C::kColXv + 4 * ks,
+                      tmem + C::kColOne, (it > 0) || (ks > 0));
+        if (!(ok = wait_or_abort(bar_dpfree, ph, abort_flag))) break;
+        if (it + 1 < n_it) {
+          const int sn = (it + 1) % C::kStages;
+          if (!(ok = wait_or_abort(full + sn, ((it + 1) / C::kStages) & 1, abort_flag))) break;
+          tc_fence_after();
+          const uint32_t qn_lo = q_lo0 + sn * (C::kTileBytes >> 4);
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks) mma_f8_ss(tmem + C::kColSd, k_lo + ks * 2, qn_lo + ks * 2, kIdesc, ks > 0);
+          tc_commit(bar_s);
+        }
+        if (!(ok = wait_or_abort(bar_pk, ph, abort_flag))) break;
+        tc_fence_after();
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks)
+          mma_mxf8_ts(tmem + C::kColDk, tmem + C::kColDc + ks * 8, q_lo + ks * 256, kIdescBs, tmem + C::kColXk + 4 * ks,
+                      tmem + C::kColOne, (it > 0) || (ks > 0));
+        tc_commit(empty + st);
+        tc_commit(bar_done);
+      }
+      if (!ok) raise_abort(abort_flag, p.status, kStatusTimeoutMma);
+    }
+  } else {
+    // ------------------------------------------------------------------------------------------ compute groups
+    const int wg = warp >> 2;                          // query blocks [wg * CH, wg * CH + CH) of every tile
+    const int quad = warp & 3;                         // lane quadrant = 32-key block of the dS scale
+    const int r = tid & 127;                           // key row inside the tile = TMEM lane
+    const int blk0 = wg * CH;
+    const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
+    const int key = kt * 128 + r;
+    const int nblk = p.N / 32;
+    const float ks_row = p.ks[static_cast<size_t>(bhk) * nblk + key / 32];
+    const float vs_row = p.vs[static_cast<size_t>(bhk) * nblk + key / 32];
+    const float2 nlog2e = splat2(-kLog2e);
+    bool ok = true;
+    // iteration state kept incrementally: stage and its phase, query tile, and the scale pointers of (head, tile)
+    int st = 0, qi = 0;
+    uint32_t st_ph = 0;
+    const float* qs_ptr = p.qs + static_cast<size_t>(b * p.H + hk * rep) * nblk + qt0 * 4 + blk0;
+    const float* dos_ptr = p.dos + static_cast<size_t>(b * p.H + hk * rep) * nblk + qt0 * 4 + blk0;
+    float qs_n[CH], dos_n[CH];
+#pragma unroll
+    for (int c = 0; c < CH; ++c) {
+      qs_n[c] = qs_ptr[c];
+      dos_n[c] = dos_ptr[c];
+    }
+    for (int it = 0; it < n_it; ++it) {
+      const uint32_t ph = it & 1;
+      const bool diag = p.causal && (qi == 0);           // the first query tile of a causal sweep is the diagonal one
+      float qs_c[CH], dos_c[CH];
+#pragma unroll
+      for (int c = 0; c < CH; ++c) {
+        qs_c[c] = qs_n[c];
+        dos_c[c] = dos_n[c];
+      }
+      {                                                  // advance to the next (head, tile) and prefetch its scales
+        const int step = (qi + 1 == n_qi) ? (nblk - (n_qi - 1) * 4) : 4;
+        qs_ptr += step;
+        dos_ptr += step;
+        if (it + 1 < n_it) {
+#pragma unroll
+          for (int c = 0; c < CH; ++c) {
+            qs_n[c] = qs_ptr[c];
+            dos_n[c] = dos_ptr[c];
+          }
+        }
+      }
+      const float* lse_s = sVec + st * 256 + 32 * blk0;
+      const float* dl_s = lse_s + 128;
+      float2 pr[CH][16];
+      if (ok) ok = wait_warp(full + st, st_ph, abort_flag);       // lse / delta of the tile are in smem
+      if (ok) ok = wait_warp(bar_s, ph, abort_flag);
+      if (ok) {
+        tc_fence_after();
+        uint32_t rs[CH][32];
+#pragma unroll
+        for (int c = 0; c < CH; ++c) tmem_ld32(tmem + lane_base + C::kColSd + 32 * (blk0 + c), rs[c]);
+        tmem_wait_ld();
+        tc_fence_before();
+        __syncwarp();
+        if ((tid & 31) == 0) mbar_arrive(bar_sfree);
+        uint32_t w[CH][8], xv[CH];
+#pragma unroll
+        for (int c = 0; c < CH; ++c) {
+          if (diag) {
+#pragma unroll
+            for (int e = 0; e < 32; ++e)
+              if (r > 32 * (blk0 + c) + e) rs[c][e] = 0xff800000u;   // -inf: key index above the query index
+          }
+          const float2 cc = splat2((ks_row * qs_c[c]) * kLog2e);
+          float pm0 = 0.f, pm1 = 0.f;
+#pragma unroll
+          for (int e = 0; e < 16; e += 2) {
+            const float4 l4 = *reinterpret_cast<const float4*>(lse_s + 32 * c + 2 * e);
+            const float2 x0 = fma2(make_float2(__uint_as_float(rs[c][2 * e]), __uint_as_float(rs[c][2 * e + 1])), cc,
+                                   mul2(make_float2(l4.x, l4.y), nlog2e));
+            const float2 x1 = fma2(make_float2(__uint_as_float(rs[c][2 * e + 2]), __uint_as_float(rs[c][2 * e + 3])), cc,
+                                   mul2(make_float2(l4.z, l4.w), nlog2e));
+            pr[c][e] = ex2_2(x0);
+            pr[c][e + 1] = ex2_2(x1);
+            pm0 = max3(pm0, pr[c][e].x, pr[c][e].y);
+            pm1 = max3(pm1, pr[c][e + 1].x, pr[c][e + 1].y);
+          }
+          // P^T codes: one power-of-two scale per (key row, 32 queries) = per thread, block and tile
+          const uint32_t psb = pow2_sb(fmaxf(pm0, pm1), 0u);
+          codes32(pr[c], sb_to_inv(psb), w[c]);
+          xv[c] = sb_mul(psb, scale_to_sb(dos_c[c]));
+        }
+        if (it > 0) ok = wait_warp(bar_done, ph ^ 1, abort_flag);   // the previous chains have read codes and words
+        if (ok) {
+#pragma unroll
+          for (int c = 0; c < CH; ++c) {
+            tmem_st8(tmem + lane_base + C::kColPc + 8 * (blk0 + c), w[c]);
+            tmem_st4(tmem + lane_base + C::kColXv + 4 * (blk0 + c), xv[c], xv[c], xv[c], xv[c]);
+          }
+          if (wg == 0) tmem_st4(tmem + lane_base + C::kColOne, 0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu);
+          tmem_wait_st();
+          tc_fence_before();
+          __syncwarp();
+          if ((tid & 31) == 0) mbar_arrive(bar_pv);
+        }
+      }
+      if (ok) ok = wait_warp(bar_dp, ph, abort_flag);
+      if (ok) {
+        tc_fence_after();
+        uint32_t rd[CH][32];
+#pragma unroll
+        for (int c = 0; c < CH; ++c) tmem_ld32(tmem + lane_base + C::kColSd + 32 * (blk0 + c), rd[c]);
+        tmem_wait_ld();
+        tc_fence_before();
+        __syncwarp();
+        if ((tid & 31) == 0) mbar_arrive(bar_dpfree);
+        float am0 = 0.f, am1 = 0.f;
+#pragma unroll
+        for (int c = 0; c < CH; ++c) {
+          // -dS = P (delta - dP_acc a): a is a power of two, so the product is exact; the sign is undone by the scale
+          const float2 naa = splat2(-(vs_row * dos_c[c]));
+#pragma unroll
+          for (int e = 0; e < 16; e += 2) {
+            const float4 d4 = *reinterpret_cast<const float4*>(dl_s + 32 * c + 2 * e);
+            const float2 t0 = fma2(make_float2(__uint_as_float(rd[c][2 * e]), __uint_as_float(rd[c][2 * e + 1])), naa,
+                                   make_float2(d4.x, d4.y));
+            const float2 t1 = fma2(make_float2(__uint_as_float(rd[c][2 * e + 2]), __uint_as_float(rd[c][2 * e + 3])), naa,
+                                   make_float2(d4.z, d4.w));
+            pr[c][e] = mul2(pr[c][e], t0);
+            pr[c][e + 1] = mul2(pr[c][e + 1], t1);
+            am0 = max3(am0, fabsf(pr[c][e].x), fabsf(pr[c][e].y));
+            am1 = max3(am1, fabsf(pr[c][e + 1].x), fabsf(pr[c][e + 1].y));
+          }
+        }
+        const float wm = warp_max(fmaxf(am0, am1));
+        if ((tid & 31) == 0) sXch[ph * 16 + warp] = wm;
+      }
+      // one dS scale per (128 queries x this quadrant's 32 keys): the groups' warps of the quadrant meet here
+      bar_sync(1 + quad, 32 * C::kGroups);         // reached in every iteration, also after a failed wait
+      const int st_cur = st;
+      if (++st == C::kStages) {
+        st = 0;
+        st_ph ^= 1;
+      }
+      if (++qi == n_qi) qi = 0;
+      (void)st_cur;
+      if (!ok) continue;
+      const float* x = sXch + ph * 16 + quad;
+      float am = fmaxf(x[0], x[4]);
+      if (C::kGroups == 4) am = fmaxf(am, fmaxf(x[8], x[12]));
+      const uint32_t dsb = pow2_sb(am, 127u);
+      const float ninv = -sb_to_inv(dsb);
+#pragma unroll
+      for (int c = 0; c < CH; ++c) {
+        uint32_t w[8];
+        codes32(pr[c], ninv, w);
+        tmem_st8(tmem + lane_base + C::kColDc + 8 * (blk0 + c), w);
+        const uint32_t xk = sb_mul(dsb, scale_to_sb(qs_c[c]));
+        tmem_st4(tmem + lane_base + C::kColXk + 4 * (blk0 + c), xk, xk, xk, xk);
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if ((tid & 31) == 0) mbar_arrive(bar_pk);
+    }
+    if (ok) ok = wait_warp(bar_done, (n_it - 1) & 1, abort_flag);
+    if (!ok) {
+      raise_abort(abort_flag, p.status, kStatusTimeoutCompute);
+    } else {
+      tc_fence_after();
+#pragma unroll 1
+      for (int c = 0; c < CH; ++c) {
+        uint32_t rr[32];
+        tmem_ld32(tmem + lane_base + C::kColDv + 32 * (blk0 + c), rr);
+        tmem_wait_ld();
+        store_bf16_chunk(rr, 1.0f, p.dv + static_cast<int64_t>(b) * p.dv_sb + static_cast<int64_t>(key) * p.dv_sn +
+                                       static_cast<int64_t>(hk) * p.dv_sh + 32 * (blk0 + c));
+        tmem_ld32(tmem + lane_base + C::kColDk + 32 * (blk0 + c), rr);
+        tmem_wait_ld();
+        store_bf16_chunk(rr, 1.0f, p.dk + static_cast<int64_t>(b) * p.dk_sb + static_cast<int64_t>(key) * p.dk_sn +
+                                       static_cast<int64_t>(hk) * p.dk_sh + 32 * (blk0 + c));
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == kW + 1) tmem_dealloc(tmem, C::kTmemCols);
+}
+
 // ================================================================================================ dQ
 template <int D>
-struct DqCfg {
+struct DqSerialCfg {
   static constexpr int kSub = D / 128;
   static constexpr int kTileBytes = 128 * D;
   static constexpr int kStages = 2;
@@ -349,9 +711,9 @@ struct DqCfg {
 
 template <int D>
 __global__ void __launch_bounds__(192, 1)
-bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+bwd_dq_serial_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
               const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do, const BwdParams p) {
-  using C = DqCfg<D>;
+  using C = DqSerialCfg<D>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem + C::kSmemQ;
@@ -429,24 +791,24 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   } else if (warp == 5) {
     if (elect_one()) {
       constexpr uint32_t kIdesc = idesc_f8(128, 128, false, false);
+      const uint32_t q_lo = desc_lo(smem_u32(sQ)), do_lo = desc_lo(smem_u32(sDo)), ds_lo = desc_lo(smem_u32(sDs));
+      const uint32_t k_lo0 = desc_lo(smem_u32(sK)), v_lo0 = desc_lo(smem_u32(sV));
       bool ok = wait_or_abort(bar_q, 0, abort_flag);
       for (int it = 0; ok && it < n_it; ++it) {
         const int st = it % C::kStages;
         if (!(ok = wait_or_abort(full + st, (it / C::kStages) & 1, abort_flag))) break;
         if (it > 0 && !(ok = wait_or_abort(bar_done, (it - 1) & 1, abort_flag))) break;
         tc_fence_after();
-        const uint32_t k_addr = smem_u32(sK + st * C::kTileBytes), v_addr = smem_u32(sV + st * C::kTileBytes);
+        const uint32_t k_lo = k_lo0 + st * (C::kTileBytes >> 4), v_lo = v_lo0 + st * (C::kTileBytes >> 4);
 #pragma unroll
         for (int ks = 0; ks < D / 32; ++ks) {
-          const uint32_t off = (ks / 4) * 16384 + (ks % 4) * 32;
-          mma_f8_ss(tmem + C::kColS, smem_desc_sw128(smem_u32(sQ) + off, 16, 1024),
-                    smem_desc_sw128(k_addr + off, 16, 1024), kIdesc, ks > 0);
+          const uint32_t off = (ks / 4) * 1024 + (ks % 4) * 2;      // descriptor units of 16 bytes
+          mma_f8_ss(tmem + C::kColS, q_lo + off, k_lo + off, kIdesc, ks > 0);
         }
 #pragma unroll
         for (int ks = 0; ks < D / 32; ++ks) {
-          const uint32_t off = (ks / 4) * 16384 + (ks % 4) * 32;
-          mma_f8_ss(tmem + C::kColDp, smem_desc_sw128(smem_u32(sDo) + off, 16, 1024),
-                    smem_desc_sw128(v_addr + off, 16, 1024), kIdesc, ks > 0);
+          const uint32_t off = (ks / 4) * 1024 + (ks % 4) * 2;
+          mma_f8_ss(tmem + C::kColDp, do_lo + off, v_lo + off, kIdesc, ks > 0);
         }
         tc_commit(bar_s);
         if (!(ok = wait_or_abort(bar_p, it & 1, abort_flag))) break;
@@ -456,8 +818,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         for (int ks = 0; ks < 4; ++ks) {
 #pragma unroll
           for (int s = 0; s < C::kSub; ++s) {
-            mma_mxf8_ss(tmem + C::kColDq + s * 128, smem_desc_sw128(smem_u32(sDs) + ks * 32, 16, 1024),
-                        smem_desc_sw128(k_addr + s * 16384 + ks * 4096, 16, 1024),
+            mma_mxf8_ss(tmem + C::kColDq + s * 128, ds_lo + ks * 2, k_lo + s * 1024 + ks * 256,
                         idesc_mxf8(128, 128, false, true, ks, ks), tmem + C::kColSfa, tmem + C::kColOne,
                         (it > 0) || (ks > 0));
           }
@@ -579,6 +940,274 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   if (warp == 5) tmem_dealloc(tmem, C::kTmemCols);
 }
 
+
+// ================================================================================================ dQ, pipelined (D = 128)
+// One CTA per SM, 576 threads.  Warps 0-15: four compute groups of four warps; group g owns key block g of every tile
+// (32 key columns = one whole dS scale block of 128 queries x 32 keys; thread t % 128 = query row = TMEM lane), which
+// puts four compute warps on every scheduler.  Warp 16: TMA.  Warp 17: MMA.  The groups pull S and dP of tile i into
+// registers and hand the accumulators back at once, so the tensor pipe computes S, dP of tile i+1 while the groups take
+// the exponentials of tile i; dS codes go to shared memory (double-buffered), the scale words to TMEM columns of their
+// own, and dQ += dS K runs behind the next tile's compute.
+struct DqCfg {
+  static constexpr int kTileBytes = 128 * 128;
+  static constexpr int kStages = 3;
+  static constexpr int kGroups = 4;
+  static constexpr int kThreads = kGroups * 128 + 64;
+  static constexpr int kTmemCols = 512;
+  static constexpr int kColS = 0, kColDp = 128, kColDq = 256;
+  static constexpr int kColX = 384;          // 4 x 4 columns: scale word of key block g at kColX + 4 g (byte 0)
+  static constexpr int kColOne = 400;        // 4 columns of 0x7F7F7F7F: scale 1.0 for the B operand
+  static constexpr int kSmemQ = 0;
+  static constexpr int kSmemDo = kTileBytes;
+  static constexpr int kSmemK = 2 * kTileBytes;
+  static constexpr int kSmemV = kSmemK + kStages * kTileBytes;
+  static constexpr int kSmemDs = kSmemV + kStages * kTileBytes;      // 2 x (128 x 128 dS codes, rows = queries)
+  static constexpr int kSmemRed = kSmemDs + 2 * kTileBytes;          // 2 x [16 warps] block maxima, then probe sums
+  static constexpr int kSmemProbe = kSmemRed + 2 * 16 * 4;           // 3 groups x 128 rows x 2 doubles
+  static constexpr int kSmemBar = kSmemProbe + 3 * 128 * 16;
+  static constexpr int kSmemBytes = kSmemBar + 256 + 1024;
+};
+
+__global__ void __launch_bounds__(DqCfg::kThreads, 1)
+bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+              const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do, const BwdParams p) {
+  using C = DqCfg;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem + C::kSmemQ;
+  uint8_t* sDo = smem + C::kSmemDo;
+  uint8_t* sK = smem + C::kSmemK;
+  uint8_t* sV = smem + C::kSmemV;
+  uint8_t* sDs = smem + C::kSmemDs;
+  float* sRed = reinterpret_cast<float*>(smem + C::kSmemRed);
+  double* sProbe = reinterpret_cast<double*>(smem + C::kSmemProbe);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kSmemBar);
+  uint64_t* bar_q = bars + 0;
+  uint64_t* bar_s = bars + 1;        // S and dP of the tile ready (MMA commit)
+  uint64_t* bar_free = bars + 2;     // every compute warp holds its part of the tile in registers (16 arrivals)
+  uint64_t* bar_p = bars + 3;        // dS codes and scale words written (16 arrivals)
+  uint64_t* bar_done = bars + 4;     // dQ chain of the tile done (MMA commit)
+  uint64_t* full = bars + 5;         // [kStages]
+  uint64_t* empty = bars + 8;        // [kStages]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 13);
+
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int n_t = p.N / 128;
+  const int qt = n_t - 1 - static_cast<int>(blockIdx.x);
+  const int bh = blockIdx.y;
+  const int b = bh / p.H, h = bh % p.H;
+  const int bhk = b * p.Hk + h / (p.H / p.Hk);
+  const int n_it = p.causal ? (qt + 1) : n_t;
+
+  if (tid == 0) {
+    mbar_init(bar_q, 1);
+    mbar_init(bar_s, 1);
+    mbar_init(bar_free, C::kGroups * 4);
+    mbar_init(bar_p, C::kGroups * 4);
+    mbar_init(bar_done, 1);
+    for (int s = 0; s < C::kStages; ++s) {
+      mbar_init(full + s, 1);
+      mbar_init(empty + s, 1);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 17) {
+    tmem_alloc(tmem_slot, C::kTmemCols);
+    tmem_relinquish();
+    tc_fence_before();
+  }
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp == 16) {
+    // ------------------------------------------------------------------------------------------ TMA producer
+    if (elect_one()) {
+      tma_prefetch_desc(&tm_q);
+      tma_prefetch_desc(&tm_k);
+      tma_prefetch_desc(&tm_v);
+      tma_prefetch_desc(&tm_do);
+      mbar_expect_tx(bar_q, 2 * C::kTileBytes);
+      tma_load_2d(sQ, &tm_q, bar_q, 0, bh * p.N + qt * 128);
+      tma_load_2d(sDo, &tm_do, bar_q, 0, bh * p.N + qt * 128);
+      for (int it = 0; it < n_it; ++it) {
+        const int st = it % C::kStages;
+        if (it >= C::kStages) {
+          if (!wait_or_abort(empty + st, ((it / C::kStages) - 1) & 1, abort_flag)) {
+            raise_abort(abort_flag, p.status, kStatusTimeoutProducer);
+            break;
+          }
+        }
+        const int row = bhk * p.N + it * 128;
+        mbar_expect_tx(full + st, 2 * C::kTileBytes);
+        tma_load_2d(sK + st * C::kTileBytes, &tm_k, full + st, 0, row);
+        tma_load_2d(sV + st * C::kTileBytes, &tm_v, full + st, 0, row);
+      }
+    }
+  } else if (warp == 17) {
+    // ------------------------------------------------------------------------------------------ MMA issuer
+    if (elect_one()) {
+      constexpr uint32_t kIdesc = idesc_f8(128, 128, false, false);
+      const uint32_t q_lo = desc_lo(smem_u32(sQ)), do_lo = desc_lo(smem_u32(sDo)), ds_lo0 = desc_lo(smem_u32(sDs));
+      const uint32_t k_lo0 = desc_lo(smem_u32(sK)), v_lo0 = desc_lo(smem_u32(sV));
+      auto issue_s_dp = [&](int st) {
+        const uint32_t k_lo = k_lo0 + st * (C::kTileBytes >> 4), v_lo = v_lo0 + st * (C::kTileBytes >> 4);
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) mma_f8_ss(tmem + C::kColS, q_lo + ks * 2, k_lo + ks * 2, kIdesc, ks > 0);
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) mma_f8_ss(tmem + C::kColDp, do_lo + ks * 2, v_lo + ks * 2, kIdesc, ks > 0);
+        tc_commit(bar_s);
+      };
+      bool ok = wait_or_abort(bar_q, 0, abort_flag);
+      if (ok) ok = wait_or_abort(full + 0, 0, abort_flag);
+      if (ok) {
+        tc_fence_after();
+        issue_s_dp(0);
+      }
+      for (int it = 0; ok && it < n_it; ++it) {
+        const int st = it % C::kStages;
+        if (!(ok = wait_or_abort(bar_free, it & 1, abort_flag))) break;
+        if (it + 1 < n_it) {
+          const int sn = (it + 1) % C::kStages;
+          if (!(ok = wait_or_abort(full + sn, ((it + 1) / C::kStages) & 1, abort_flag))) break;
+          tc_fence_after();
+          issue_s_dp(sn);
+        }
+        if (!(ok = wait_or_abort(bar_p, it & 1, abort_flag))) break;
+        tc_fence_after();
+        // dQ += dS K: A = dS codes in shared memory (rows = queries, K-major), B = K tile MN-major (32 key rows per step)
+        const uint32_t ds_lo = ds_lo0 + (it & 1) * (C::kTileBytes >> 4), k_lo = k_lo0 + st * (C::kTileBytes >> 4);
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks)
+          mma_mxf8_ss(tmem + C::kColDq, ds_lo + ks * 2, k_lo + ks * 256, idesc_mxf8(128, 128, false, true, 0, 0),
+                      tmem + C::kColX + 4 * ks, tmem + C::kColOne, (it > 0) || (ks > 0));
+        tc_commit(empty + st);
+        tc_commit(bar_done);
+      }
+      if (!ok) raise_abort(abort_flag, p.status, kStatusTimeoutMma);
+    }
+  } else {
+    // ------------------------------------------------------------------------------------------ compute groups
+    const int wg = warp >> 2;
+    const int r = tid & 127;
+    const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const int row = qt * 128 + r;
+    const int nblk = p.N / 32;
+    const float qs = p.qs[static_cast<size_t>(bh) * nblk + row / 32];
+    const float dos = p.dos[static_cast<size_t>(bh) * nblk + row / 32];
+    const float2 nl2 = splat2(-(p.lse[static_cast<size_t>(bh) * p.N + row] * kLog2e));
+    const float2 ndl = splat2(-p.delta[static_cast<size_t>(bh) * p.N + row]);
+    const bool probe = p.rowsum_ds != nullptr;
+    const float* ks_base = p.ks + static_cast<size_t>(bhk) * nblk + wg;
+    const float* vs_base = p.vs + static_cast<size_t>(bhk) * nblk + wg;
+    float ks1 = *ks_base, vs1 = *vs_base;
+    double rs_acc = 0.0, ap_acc = 0.0;
+    bool ok = true;
+    for (int it = 0; it < n_it; ++it) {
+      const float ksv = ks1, vsv = vs1;
+      if (it + 1 < n_it) {
+        ks1 = ks_base[(it + 1) * 4];
+        vs1 = vs_base[(it + 1) * 4];
+      }
+      const bool diag = p.causal && (it == qt);
+      float2 v[16];
+      if (ok) ok = wait_warp(bar_s, it & 1, abort_flag);
+      if (ok) {
+        tc_fence_after();
+        uint32_t rs[32], rd[32];
+        tmem_ld32(tmem + lane_base + C::kColS + 32 * wg, rs);
+        tmem_ld32(tmem + lane_base + C::kColDp + 32 * wg, rd);
+        tmem_wait_ld();
+        tc_fence_before();
+        __syncwarp();
+        if ((tid & 31) == 0) mbar_arrive(bar_free);    // this warp's part of the accumulators may be overwritten now
+        if (diag) {
+#pragma unroll
+          for (int e = 0; e < 32; ++e)
+            if (32 * wg + e > r) rs[e] = 0xff800000u;  // -inf: key index above the query index
+        }
+        const float2 cc = splat2((ksv * qs) * kLog2e), aa = splat2(vsv * dos);
+        float am0 = 0.f, am1 = 0.f;
+        float2 rsum = make_float2(0.f, 0.f), asum = rsum;
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+          const float2 pe = ex2_2(fma2(make_float2(__uint_as_float(rs[2 * e]), __uint_as_float(rs[2 * e + 1])), cc, nl2));
+          const float2 dp = make_float2(__uint_as_float(rd[2 * e]), __uint_as_float(rd[2 * e + 1]));
+          const float2 t = fma2(dp, aa, ndl);          // dP_acc * a - delta: a is a power of two, the product is exact
+          const float2 d = mul2(pe, t);
+          v[e] = d;
+          if (e & 1) am1 = max3(am1, fabsf(d.x), fabsf(d.y));
+          else am0 = max3(am0, fabsf(d.x), fabsf(d.y));
+          if (probe) {
+            rsum = add2(rsum, d);
+            const float2 pd = mul2(pe, mul2(dp, aa));
+            asum = add2(asum, make_float2(fabsf(pd.x), fabsf(pd.y)));
+          }
+        }
+        if (probe) {
+          rs_acc += static_cast<double>(rsum.x) + static_cast<double>(rsum.y);
+          ap_acc += static_cast<double>(asum.x) + static_cast<double>(asum.y);
+        }
+        // one scale per (128 queries x 32 keys): the maxima of this group's four warps meet in shared memory
+        const float wm = warp_max(fmaxf(am0, am1));
+        if ((tid & 31) == 0) sRed[(it & 1) * 16 + warp] = wm;
+      }
+      bar_sync(1 + wg, 128);          // reached by every warp of the group in every iteration, also after a failed wait
+      if (ok && it > 0) ok = wait_warp(bar_done, (it - 1) & 1, abort_flag);   // the previous chain has read its scale words
+      if (!ok) continue;
+      const float* red = sRed + (it & 1) * 16 + wg * 4;
+      const uint32_t dsb = pow2_sb(fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3])), 127u);
+      uint32_t w[8];
+      codes32(v, sb_to_inv(dsb), w);
+      // row r of the dS tile: 16-byte chunk j of the row lands at chunk (j ^ (r % 8)) (128-byte swizzle)
+      uint8_t* ds_row = sDs + (it & 1) * C::kTileBytes + r * 128;
+      *reinterpret_cast<uint4*>(ds_row + (((2 * wg) ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+      *reinterpret_cast<uint4*>(ds_row + (((2 * wg + 1) ^ (r & 7)) << 4)) = make_uint4(w[4], w[5], w[6], w[7]);
+      const uint32_t word = sb_mul(dsb, scale_to_sb(ksv));
+      tmem_st4(tmem + lane_base + C::kColX + 4 * wg, word, word, word, word);
+      if (wg == 0) tmem_st4(tmem + lane_base + C::kColOne, 0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu);
+      tmem_wait_st();
+      fence_async_smem();
+      tc_fence_before();
+      __syncwarp();
+      if ((tid & 31) == 0) mbar_arrive(bar_p);
+    }
+    if (ok) ok = wait_warp(bar_done, (n_it - 1) & 1, abort_flag);
+    if (!ok) raise_abort(abort_flag, p.status, kStatusTimeoutCompute);
+    if (ok) {
+      tc_fence_after();
+      __nv_bfloat16* dst = p.dq + static_cast<int64_t>(b) * p.dq_sb + static_cast<int64_t>(row) * p.dq_sn +
+                           static_cast<int64_t>(h) * p.dq_sh + 32 * wg;
+      uint32_t rr[32];
+      tmem_ld32(tmem + lane_base + C::kColDq + 32 * wg, rr);
+      tmem_wait_ld();
+      store_bf16_chunk(rr, p.sm_scale, dst);
+    }
+    if (probe) {                       // identity probe: the groups' partial row sums meet in shared memory
+      if (wg > 0) {
+        sProbe[((wg - 1) * 128 + r) * 2] = rs_acc;
+        sProbe[((wg - 1) * 128 + r) * 2 + 1] = ap_acc;
+        bar_arrive(5, C::kGroups * 128);
+      } else {
+        bar_sync(5, C::kGroups * 128);
+        for (int g = 0; g < C::kGroups - 1; ++g) {
+          rs_acc += sProbe[(g * 128 + r) * 2];
+          ap_acc += sProbe[(g * 128 + r) * 2 + 1];
+        }
+        if (ok) {
+          p.rowsum_ds[static_cast<size_t>(bh) * p.N + row] = static_cast<float>(rs_acc);
+          p.sum_abs_pdp[static_cast<size_t>(bh) * p.N + row] = static_cast<float>(ap_acc);
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 17) tmem_dealloc(tmem, C::kTmemCols);
+}
+
 // ================================================================================================ launchers
 template <typename K>
 static cudaError_t set_smem(K kernel, int bytes, bool* done) {
@@ -606,7 +1235,27 @@ static cudaError_t launch_kv_t(const CUtensorMap& tq, const CUtensorMap& tk, con
 
 cudaError_t launch_bwd_dkdv(int D, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                             const CUtensorMap& tdo, const BwdParams& p, cudaStream_t stream) {
-  if (D == 128) return launch_kv_t<128, true, true>(tq, tk, tv, tdo, p, stream);
+  if (D == 128) {
+    // DM_KV_GROUPS (tuning): compute groups of the pipelined kernel, 4 (32 query columns per thread; default, 1.26 ms at
+    // B=4 N=4096 H=32 Hk=8 on B200) or 2 (64 columns per thread, 1.30 ms)
+    static const int groups = [] {
+      const char* e = getenv("DM_KV_GROUPS");
+      return (e != nullptr && e[0] == '2') ? 2 : 4;
+    }();
+    dim3 grid(p.N / 128, p.B * p.Hk);
+    if (groups == 4) {
+      static bool done[64] = {};
+      cudaError_t e = set_smem(bwd_dkdv_pipe_kernel<4>, KvPipeCfg<4>::kSmemBytes, done);
+      if (e != cudaSuccess) return e;
+      bwd_dkdv_pipe_kernel<4><<<grid, KvPipeCfg<4>::kThreads, KvPipeCfg<4>::kSmemBytes, stream>>>(tq, tk, tv, tdo, p);
+    } else {
+      static bool done[64] = {};
+      cudaError_t e = set_smem(bwd_dkdv_pipe_kernel<2>, KvPipeCfg<2>::kSmemBytes, done);
+      if (e != cudaSuccess) return e;
+      bwd_dkdv_pipe_kernel<2><<<grid, KvPipeCfg<2>::kThreads, KvPipeCfg<2>::kSmemBytes, stream>>>(tq, tk, tv, tdo, p);
+    }
+    return cudaGetLastError();
+  }
   // head_dim 256: S^T + dP^T + dK + dV exceed the 512 TMEM columns, so dV and dK run as two launches
   cudaError_t e = launch_kv_t<256, true, false>(tq, tk, tv, tdo, p, stream);
   if (e != cudaSuccess) return e;
@@ -614,20 +1263,28 @@ cudaError_t launch_bwd_dkdv(int D, const CUtensorMap& tq, const CUtensorMap& tk,
 }
 
 template <int D>
-static cudaError_t launch_dq_t(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
-                               const CUtensorMap& tdo, const BwdParams& p, cudaStream_t stream) {
-  using C = DqCfg<D>;
+static cudaError_t launch_dq_serial_t(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
+                                      const CUtensorMap& tdo, const BwdParams& p, cudaStream_t stream) {
+  using C = DqSerialCfg<D>;
   static bool done[64] = {};
-  cudaError_t e = set_smem(bwd_dq_kernel<D>, C::kSmemBytes, done);
+  cudaError_t e = set_smem(bwd_dq_serial_kernel<D>, C::kSmemBytes, done);
   if (e != cudaSuccess) return e;
   dim3 grid(p.N / 128, p.B * p.H);
-  bwd_dq_kernel<D><<<grid, 192, C::kSmemBytes, stream>>>(tq, tk, tv, tdo, p);
+  bwd_dq_serial_kernel<D><<<grid, 192, C::kSmemBytes, stream>>>(tq, tk, tv, tdo, p);
   return cudaGetLastError();
 }
 
 cudaError_t launch_bwd_dq(int D, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                           const CUtensorMap& tdo, const BwdParams& p, cudaStream_t stream) {
-  return D == 128 ? launch_dq_t<128>(tq, tk, tv, tdo, p, stream) : launch_dq_t<256>(tq, tk, tv, tdo, p, stream);
+  // head_dim 256: dQ alone fills 256 TMEM columns, which leaves no room for the pipelined kernel's separate scale-word
+  // columns; it keeps the kernel that serialises MMA and compute inside a CTA.
+  if (D != 128) return launch_dq_serial_t<256>(tq, tk, tv, tdo, p, stream);
+  static bool done[64] = {};
+  cudaError_t e = set_smem(bwd_dq_kernel, DqCfg::kSmemBytes, done);
+  if (e != cudaSuccess) return e;
+  dim3 grid(p.N / 128, p.B * p.H);
+  bwd_dq_kernel<<<grid, DqCfg::kThreads, DqCfg::kSmemBytes, stream>>>(tq, tk, tv, tdo, p);
+  return cudaGetLastError();
 }
 
 }  // namespace dm

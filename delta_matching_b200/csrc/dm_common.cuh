@@ -40,6 +40,15 @@ __device__ __forceinline__ uint32_t pack4(uint32_t b0, uint32_t b1, uint32_t b2,
   return b0 | (b1 << 8) | (b2 << 16) | (b3 << 24);
 }
 
+// (hi, lo) += x with the rounding error of the addition kept in lo (Knuth TwoSum; no fast-math reassociation is enabled).
+__device__ __forceinline__ void two_sum_acc(float& hi, float& lo, float x) {
+  const float s = __fadd_rn(hi, x);
+  const float bb = __fsub_rn(s, hi);
+  const float err = __fadd_rn(__fsub_rn(hi, __fsub_rn(s, bb)), __fsub_rn(x, bb));
+  hi = s;
+  lo = __fadd_rn(lo, err);
+}
+
 // ---------------------------------------------------------------------------------------------- bounded waits
 __device__ __forceinline__ uint64_t global_ns() {
   uint64_t t;
@@ -52,13 +61,21 @@ __device__ __forceinline__ uint64_t global_ns() {
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
 __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
   if (mbar_try_wait(bar, parity)) return true;
+  // A waiting warp must not eat the issue slots of the warps it waits for: after a few immediate retries it sleeps
+  // between polls, and it looks at the abort flag and the clock only every 256 polls.
+#pragma unroll 1
+  for (int i = 0; i < 4; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+  }
   const uint64_t t0 = global_ns();
-  for (;;) {
-    for (int i = 0; i < 64; ++i) {
-      if (mbar_try_wait(bar, parity)) return true;
+#pragma unroll 1
+  for (uint32_t spins = 1;; ++spins) {
+    __nanosleep(40);
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((spins & 255u) == 0u) {
+      if (*abort_flag != 0) return false;
+      if (global_ns() - t0 > kWaitLimitNs) return false;
     }
-    if (*abort_flag != 0) return false;
-    if (global_ns() - t0 > kWaitLimitNs) return false;
   }
 }
 // Whole-warp form for the compute warps: every lane polls, the verdict is made uniform so that the warp-wide tcgen05.ld /
@@ -71,7 +88,13 @@ __device__ __forceinline__ void raise_abort(volatile int* abort_flag, int* statu
   if (status != nullptr) atomicCAS(status, 0, code);
 }
 
-// 128-thread named barrier for the compute warps (id 1..15; id 0 is __syncthreads).
+// Producer side of a named barrier: count towards the barrier without waiting (the consumers call bar_sync with the
+// same id and total thread count).
+__device__ __forceinline__ void bar_arrive(int id, int nthreads) {
+  asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+
+// Named barrier for the compute warps (id 1..15; id 0 is __syncthreads).
 __device__ __forceinline__ void bar_sync(int id, int nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }

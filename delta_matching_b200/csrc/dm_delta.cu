@@ -4,11 +4,17 @@
 // Arithmetic shared with the backward (delta_matching/sm100/attention_math_sm100.py:26-45; emulation
 // delta_matching/reference.py:483, 491, 526-535):
 //   c = (ks_b * qs) * log2e;  l2 = lse * log2e;  P = ex2(fma(S_acc, c, -l2));  a = vs_b * dos;  dP = dP_acc * a.
-// Sums: four fp32 FMA chains of 8 elements per 32-key block, folded into fp64 per row (the power-of-two factor a is
-// applied once per block, which is exact); one fp64 divide and one fp32 store per row.
+// Sums: four fp32 FMA chains of 8 elements per 32-key block (the power-of-two factor a is applied once per block,
+// which is exact), block sums accumulated across key tiles as compensated fp32 pairs (TwoSum), folded in fp64 at the
+// end; one fp64 divide and one fp32 store per row.
 //
-// CTA = one 128-query tile of one (batch, query head); S = Q8 K8^T and dP = dO8 V8^T on tcgen05 (kind::f8f6f4) into
-// two 128-column TMEM accumulators.  Warps 0-3 compute (thread t = TMEM lane t = query row t), warp 4 TMA, warp 5 MMA.
+// CTA = one 128-query tile of one (batch, query head), one CTA per SM.  S = Q8 K8^T and dP = dO8 V8^T run on tcgen05
+// (kind::f8f6f4) into TMEM accumulators that are double-buffered (2 x (128 + 128) columns), so the tensor pipe works on
+// key tile i+1 while the compute warps take the exponentials of tile i.  Four compute groups of four warps (warps 0-15)
+// split the 128 key columns of a tile, 32 each, i.e. one K/V scale block per group (thread t of every group = TMEM lane
+// t % 128 = query row), which puts four compute warps on every scheduler: enough to keep the MUFU pipe fed while one
+// warp waits for TMEM or an mbarrier.  Warp 16 issues TMA loads, warp 17 the MMAs.  The four partial sums of a row meet
+// once, at the end, in shared memory.
 #include "dm_common.cuh"
 #include "dm_kernels.h"
 
@@ -18,19 +24,21 @@ template <int D>
 struct DeltaCfg {
   static constexpr int kSub = D / 128;
   static constexpr int kTileBytes = 128 * D;
-  static constexpr int kStages = 2;
-  static constexpr int kTmemCols = 256;
-  static constexpr int kColS = 0, kColDp = 128;
+  static constexpr int kStages = (D == 128) ? 3 : 2;
+  static constexpr int kTmemCols = 512;
   static constexpr int kSmemQ = 0;
   static constexpr int kSmemDo = kTileBytes;
   static constexpr int kSmemK = 2 * kTileBytes;
   static constexpr int kSmemV = kSmemK + kStages * kTileBytes;
-  static constexpr int kSmemBar = kSmemV + kStages * kTileBytes;
+  static constexpr int kGroups = 4;                                     // compute groups, 32 key columns each
+  static constexpr int kThreads = kGroups * 128 + 64;
+  static constexpr int kSmemRed = kSmemV + kStages * kTileBytes;        // 3 x 128 rows x (num, den) doubles
+  static constexpr int kSmemBar = kSmemRed + 3 * 128 * 16;
   static constexpr int kSmemBytes = kSmemBar + 256 + 1024;
 };
 
 template <int D>
-__global__ void __launch_bounds__(192, (D == 128) ? 2 : 1)
+__global__ void __launch_bounds__(DeltaCfg<D>::kThreads, 1)
 delta_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
              const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do, const DeltaParams p) {
   using C = DeltaCfg<D>;
@@ -40,14 +48,15 @@ delta_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ C
   uint8_t* sDo = smem + C::kSmemDo;
   uint8_t* sK = smem + C::kSmemK;
   uint8_t* sV = smem + C::kSmemV;
+  double* sRed = reinterpret_cast<double*>(smem + C::kSmemRed);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kSmemBar);
   uint64_t* bar_q = bars + 0;
-  uint64_t* bar_s = bars + 1;      // S and dP accumulators ready
-  uint64_t* bar_c = bars + 2;      // compute warps have read them (128 arrivals)
-  uint64_t* full = bars + 4;       // [kStages] K and V of the stage landed
-  uint64_t* empty = bars + 6;      // [kStages]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 11);
+  uint64_t* bar_s = bars + 1;      // [2] S and dP of the buffer ready (MMA commit)
+  uint64_t* bar_c = bars + 3;      // [2] every compute warp has loaded its part of the buffer (16 arrivals)
+  uint64_t* full = bars + 5;       // [kStages] K and V of the stage landed
+  uint64_t* empty = bars + 8;      // [kStages] the MMAs reading the stage are done
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 13);
 
   const int tid = threadIdx.x, warp = tid >> 5;
   const int n_qt = p.N / 128;
@@ -59,8 +68,10 @@ delta_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ C
 
   if (tid == 0) {
     mbar_init(bar_q, 1);
-    mbar_init(bar_s, 1);
-    mbar_init(bar_c, 128);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(bar_s + s, 1);
+      mbar_init(bar_c + s, C::kGroups * 4);              // one arrival per compute warp
+    }
     for (int s = 0; s < C::kStages; ++s) {
       mbar_init(full + s, 1);
       mbar_init(empty + s, 1);
@@ -68,7 +79,7 @@ delta_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ C
     *abort_flag = 0;
     mbar_fence_init();
   }
-  if (warp == 5) {
+  if (warp == 17) {
     tmem_alloc(tmem_slot, C::kTmemCols);
     tmem_relinquish();
     tc_fence_before();
@@ -77,7 +88,8 @@ delta_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ C
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
 
-  if (warp == 4) {
+  if (warp == 16) {
+    // ------------------------------------------------------------------------------------------ TMA producer
     if (elect_one()) {
       tma_prefetch_desc(&tm_q);
       tma_prefetch_desc(&tm_k);
@@ -104,103 +116,113 @@ delta_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ C
         }
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == 17) {
+    // ------------------------------------------------------------------------------------------ MMA issuer
     if (elect_one()) {
       constexpr uint32_t kIdesc = idesc_f8(128, 128, false, false);
+      const uint32_t q_lo = desc_lo(smem_u32(sQ)), do_lo = desc_lo(smem_u32(sDo));
+      const uint32_t k_lo0 = desc_lo(smem_u32(sK)), v_lo0 = desc_lo(smem_u32(sV));
       bool ok = wait_or_abort(bar_q, 0, abort_flag);
       for (int it = 0; ok && it < n_it; ++it) {
-        const int st = it % C::kStages;
+        const int st = it % C::kStages, buf = it & 1;
+        // the accumulator pair `buf` was last used by tile it-2: wait until both compute groups have read it
+        if (it >= 2 && !(ok = wait_or_abort(bar_c + buf, ((it - 2) >> 1) & 1, abort_flag))) break;
         if (!(ok = wait_or_abort(full + st, (it / C::kStages) & 1, abort_flag))) break;
-        if (it > 0 && !(ok = wait_or_abort(bar_c, (it - 1) & 1, abort_flag))) break;
         tc_fence_after();
+        const uint32_t k_lo = k_lo0 + st * (C::kTileBytes >> 4), v_lo = v_lo0 + st * (C::kTileBytes >> 4);
+        const uint32_t t_s = tmem + buf * 256, t_dp = t_s + 128;
 #pragma unroll
         for (int ks = 0; ks < D / 32; ++ks) {
-          const uint32_t off = (ks / 4) * 16384 + (ks % 4) * 32;
-          mma_f8_ss(tmem + C::kColS, smem_desc_sw128(smem_u32(sQ) + off, 16, 1024),
-                    smem_desc_sw128(smem_u32(sK + st * C::kTileBytes) + off, 16, 1024), kIdesc, ks > 0);
+          const uint32_t off = (ks / 4) * 1024 + (ks % 4) * 2;      // descriptor units of 16 bytes
+          mma_f8_ss(t_s, q_lo + off, k_lo + off, kIdesc, ks > 0);
         }
 #pragma unroll
         for (int ks = 0; ks < D / 32; ++ks) {
-          const uint32_t off = (ks / 4) * 16384 + (ks % 4) * 32;
-          mma_f8_ss(tmem + C::kColDp, smem_desc_sw128(smem_u32(sDo) + off, 16, 1024),
-                    smem_desc_sw128(smem_u32(sV + st * C::kTileBytes) + off, 16, 1024), kIdesc, ks > 0);
+          const uint32_t off = (ks / 4) * 1024 + (ks % 4) * 2;
+          mma_f8_ss(t_dp, do_lo + off, v_lo + off, kIdesc, ks > 0);
         }
         tc_commit(empty + st);
-        tc_commit(bar_s);
+        tc_commit(bar_s + buf);
       }
       if (!ok) raise_abort(abort_flag, p.status, kStatusTimeoutMma);
     }
   } else {
-    const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
-    const int row = qt * 128 + tid;
+    // ------------------------------------------------------------------------------------------ compute groups
+    const int wg = warp >> 2;                          // key columns [32 wg, 32 wg + 32) of every tile: scale block wg
+    const int r = tid & 127;                           // query row inside the tile = TMEM lane
+    const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const int row = qt * 128 + r;
     const int nblk = p.N / 32;
     const float qs = p.qs[static_cast<size_t>(bh) * nblk + row / 32];
     const float dos = p.dos[static_cast<size_t>(bh) * nblk + row / 32];
-    const float neg_l2 = -(p.lse[static_cast<size_t>(bh) * p.N + row] * kLog2e);
-    double num = 0.0, den = 0.0;
+    const float2 nl2 = splat2(-(p.lse[static_cast<size_t>(bh) * p.N + row] * kLog2e));
+    const float* ks_base = p.ks + static_cast<size_t>(bhk) * nblk + wg;
+    const float* vs_base = p.vs + static_cast<size_t>(bhk) * nblk + wg;
+    float ks1 = *ks_base, vs1 = *vs_base;
+    // running sums as unevaluated fp32 pairs (hi + lo, TwoSum): exact to ~2^-48 relative without touching the fp64 pipe
+    float num_hi = 0.f, num_lo = 0.f, den_hi = 0.f, den_lo = 0.f;
     bool ok = true;
-    const float* ks_base = p.ks + static_cast<size_t>(bhk) * nblk;
-    const float* vs_base = p.vs + static_cast<size_t>(bhk) * nblk;
-    float4 ks4 = *reinterpret_cast<const float4*>(ks_base);
-    float4 vs4 = *reinterpret_cast<const float4*>(vs_base);
-    const float2 nl2 = splat2(neg_l2);
     for (int it = 0; it < n_it; ++it) {
-      const float cb[4] = {(ks4.x * qs) * kLog2e, (ks4.y * qs) * kLog2e, (ks4.z * qs) * kLog2e, (ks4.w * qs) * kLog2e};
+      const int buf = it & 1;
+      const float2 c2 = splat2((ks1 * qs) * kLog2e);
       // a = vs * dos is a power of two, so P * (dP_acc * a) == (P * dP_acc) * a exactly: a is applied once per block
-      const double ab[4] = {static_cast<double>(vs4.x * dos), static_cast<double>(vs4.y * dos),
-                            static_cast<double>(vs4.z * dos), static_cast<double>(vs4.w * dos)};
-      if (it + 1 < n_it) {
-        ks4 = *reinterpret_cast<const float4*>(ks_base + (it + 1) * 4);
-        vs4 = *reinterpret_cast<const float4*>(vs_base + (it + 1) * 4);
+      const float a = vs1 * dos;
+      if (it + 1 < n_it) {                             // scales of the next key tile, in flight during this one
+        ks1 = ks_base[(it + 1) * 4];
+        vs1 = vs_base[(it + 1) * 4];
       }
       const bool diag = p.causal && (it == qt);
-      if (!(ok = wait_warp(bar_s, it & 1, abort_flag))) break;
+      if (!(ok = wait_warp(bar_s + buf, (it >> 1) & 1, abort_flag))) break;
       tc_fence_after();
-      uint32_t rs[2][32], rd[2][32];
-      tmem_ld32(tmem + lane_base + C::kColS, rs[0]);
-      tmem_ld32(tmem + lane_base + C::kColDp, rd[0]);
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        tmem_wait_ld();
-        if (c < 3) {
-          tmem_ld32(tmem + lane_base + C::kColS + 32 * (c + 1), rs[(c + 1) & 1]);
-          tmem_ld32(tmem + lane_base + C::kColDp + 32 * (c + 1), rd[(c + 1) & 1]);
-        }
-        uint32_t(&s)[32] = rs[c & 1];
-        const uint32_t(&dp)[32] = rd[c & 1];
-        if (diag) {
-#pragma unroll
-          for (int e = 0; e < 32; ++e)
-            if (32 * c + e > tid) s[e] = 0xff800000u;
-        }
-        const float2 c2 = splat2(cb[c]);
-        float2 n0 = make_float2(0.f, 0.f), n1 = n0, d0 = n0, d1 = n0;
-#pragma unroll
-        for (int e = 0; e < 16; e += 2) {
-          const float2 p0 = ex2_2(fma2(make_float2(__uint_as_float(s[2 * e]), __uint_as_float(s[2 * e + 1])), c2, nl2));
-          const float2 p1 = ex2_2(fma2(make_float2(__uint_as_float(s[2 * e + 2]), __uint_as_float(s[2 * e + 3])), c2, nl2));
-          n0 = fma2(p0, make_float2(__uint_as_float(dp[2 * e]), __uint_as_float(dp[2 * e + 1])), n0);
-          n1 = fma2(p1, make_float2(__uint_as_float(dp[2 * e + 2]), __uint_as_float(dp[2 * e + 3])), n1);
-          d0 = add2(d0, p0);
-          d1 = add2(d1, p1);
-        }
-        num += (static_cast<double>(n0.x) + static_cast<double>(n0.y) + static_cast<double>(n1.x) +
-                static_cast<double>(n1.y)) * ab[c];
-        den += static_cast<double>(d0.x) + static_cast<double>(d0.y) + static_cast<double>(d1.x) +
-               static_cast<double>(d1.y);
-      }
+      uint32_t s[32], dp[32];
+      tmem_ld32(tmem + lane_base + buf * 256 + 32 * wg, s);
+      tmem_ld32(tmem + lane_base + buf * 256 + 128 + 32 * wg, dp);
+      tmem_wait_ld();
       tc_fence_before();
-      mbar_arrive(bar_c);
+      __syncwarp();
+      if ((tid & 31) == 0) mbar_arrive(bar_c + buf);   // this warp's part of the buffer is in registers: hand it back
+      if (diag) {
+#pragma unroll
+        for (int e = 0; e < 32; ++e)
+          if (32 * wg + e > r) s[e] = 0xff800000u;     // -inf: key index above the query index
+      }
+      float2 n0 = make_float2(0.f, 0.f), n1 = n0, d0 = n0, d1 = n0;
+#pragma unroll
+      for (int e = 0; e < 16; e += 2) {
+        const float2 p0 = ex2_2(fma2(make_float2(__uint_as_float(s[2 * e]), __uint_as_float(s[2 * e + 1])), c2, nl2));
+        const float2 p1 = ex2_2(fma2(make_float2(__uint_as_float(s[2 * e + 2]), __uint_as_float(s[2 * e + 3])), c2, nl2));
+        n0 = fma2(p0, make_float2(__uint_as_float(dp[2 * e]), __uint_as_float(dp[2 * e + 1])), n0);
+        n1 = fma2(p1, make_float2(__uint_as_float(dp[2 * e + 2]), __uint_as_float(dp[2 * e + 3])), n1);
+        d0 = add2(d0, p0);
+        d1 = add2(d1, p1);
+      }
+      const float nb = ((n0.x + n0.y) + (n1.x + n1.y)) * a;
+      const float db = (d0.x + d0.y) + (d1.x + d1.y);
+      two_sum_acc(num_hi, num_lo, nb);
+      two_sum_acc(den_hi, den_lo, db);
     }
-    if (!ok) {
-      raise_abort(abort_flag, p.status, kStatusTimeoutCompute);
+    if (!ok) raise_abort(abort_flag, p.status, kStatusTimeoutCompute);
+    // fold the groups' partial sums in fp64: groups 1-3 publish, group 0 adds in group order and stores
+    const double num = static_cast<double>(num_hi) + static_cast<double>(num_lo);
+    const double den = static_cast<double>(den_hi) + static_cast<double>(den_lo);
+    if (wg > 0) {
+      sRed[((wg - 1) * 128 + r) * 2] = num;
+      sRed[((wg - 1) * 128 + r) * 2 + 1] = den;
+      bar_arrive(1, C::kGroups * 128);
     } else {
-      p.delta[static_cast<size_t>(bh) * p.N + row] = static_cast<float>(num / den);
+      bar_sync(1, C::kGroups * 128);
+      double n = num, dd = den;
+#pragma unroll
+      for (int g = 0; g < C::kGroups - 1; ++g) {
+        n += sRed[(g * 128 + r) * 2];
+        dd += sRed[(g * 128 + r) * 2 + 1];
+      }
+      if (ok) p.delta[static_cast<size_t>(bh) * p.N + row] = static_cast<float>(n / dd);
     }
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) tmem_dealloc(tmem, C::kTmemCols);
+  if (warp == 17) tmem_dealloc(tmem, C::kTmemCols);
 }
 
 template <int D>
@@ -216,7 +238,7 @@ static cudaError_t launch_delta_t(const CUtensorMap& tq, const CUtensorMap& tk, 
     attr_set[dev] = true;
   }
   dim3 grid(p.N / 128, p.B * p.H);
-  delta_kernel<D><<<grid, 192, C::kSmemBytes, stream>>>(tq, tk, tv, tdo, p);
+  delta_kernel<D><<<grid, C::kThreads, C::kSmemBytes, stream>>>(tq, tk, tv, tdo, p);
   return cudaGetLastError();
 }
 

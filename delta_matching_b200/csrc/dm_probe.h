@@ -18,6 +18,8 @@ struct ProbeParams {
   int* status;
 };
 
+cudaError_t launch_mma_cycles(const CUtensorMap& ta, const CUtensorMap& tb, const ProbeParams& p, int n_cols, int repeat,
+                              unsigned long long* cycles, cudaStream_t stream);
 cudaError_t launch_probe(const CUtensorMap& ta, const CUtensorMap& tb, const ProbeParams& p, cudaStream_t stream);
 
 }  // namespace dm

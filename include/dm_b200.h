@@ -119,6 +119,12 @@ int dm_bwd_parts(const void* q8, const void* k8, const void* v8, const void* do8
 int dm_dbg_mma_tile(const void* a, const void* b, const uint32_t* sfa, const uint32_t* sfb, int a_tmem, int a_mn,
                     int b_mn, int scaled, int nk, float* out, int* status, void* stream);
 
+/* Timing companion of dm_dbg_mma_tile (unit-test / tuning hook, no counterpart in the reference): `repeat` groups of nk
+ * MMAs of width n_cols issued back to back into one accumulator by one CTA.  cycles (device, 5 x uint64): [0] first
+ * issue -> completion, [1] issue only, [2] one 32-column TMEM load + wait, [3] one MMA + commit round trip. */
+int dm_dbg_mma_cycles(const void* a, const void* b, int a_tmem, int a_mn, int b_mn, int scaled, int nk, int n_cols,
+                      int repeat, unsigned long long* cycles, int* status, void* stream);
+
 /* K mean without a workspace argument, for callers that cannot allocate device memory themselves (code inside a
  * no-allocation region of its host framework, or a plugin that owns no memory pool): same inputs, same kernels and
  * bit-identical result as dm_kmean, but the chunk-sum scratch is an array built into the library (4 MiB on every GPU
