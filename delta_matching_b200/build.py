@@ -1,6 +1,6 @@
 """Build the CUDA library in-tree: nvcc for sm_100a only, one shared object `libdm_b200.so` next to this file.
 
-    python -m delta_matching_b200.build [--force] [--verbose]
+    python -m delta_matching_b200.build [--force] [--verbose] [--profile]
 
 The library exports the C ABI declared in include/dm_b200.h and links only against the CUDA runtime (the driver entry
 point for tensor-map encoding is resolved at run time), so it builds on a machine without a GPU.
@@ -47,18 +47,24 @@ def code_sha() -> str:
     return h.hexdigest()[:12]
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
-    os.makedirs(OBJ, exist_ok=True)
-    stamp = os.path.join(OBJ, "stamp.txt")
+def build(force: bool = False, verbose: bool = False, profile: bool = False) -> str:
+    """Compile and link.  profile=True builds `libdm_b200_prof.so` with -DDM_PROFILE (section cycle counters inside the
+    forward and dK/dV kernels, read back with dm_prof_read_fwd / dm_prof_read_kv; load it with DM_SO): a tuning aid,
+    never the library the package loads by default."""
+    obj_dir = OBJ + ("_prof" if profile else "")
+    lib = LIB.replace(".so", "_prof.so") if profile else LIB
+    os.makedirs(obj_dir, exist_ok=True)
+    stamp = os.path.join(obj_dir, "stamp.txt")
     sha = code_sha()
-    if not force and os.path.isfile(LIB) and os.path.isfile(stamp) and open(stamp).read().strip() == sha:
-        return LIB
+    if not force and os.path.isfile(lib) and os.path.isfile(stamp) and open(stamp).read().strip() == sha:
+        return lib
     srcs = list(SOURCES)
     nvcc = _nvcc()
+    flags = NVCC_FLAGS + (["-DDM_PROFILE"] if profile else [])
 
     def compile_one(src):
-        obj = os.path.join(OBJ, src[:-3] + ".o")
-        cmd = [nvcc, *NVCC_FLAGS, "-c", os.path.join(CSRC, src), "-o", obj]
+        obj = os.path.join(obj_dir, src[:-3] + ".o")
+        cmd = [nvcc, *flags, "-c", os.path.join(CSRC, src), "-o", obj]
         if verbose:
             cmd.insert(1, "-Xptxas")
             cmd.insert(2, "-v")
@@ -71,13 +77,13 @@ def build(force: bool = False, verbose: bool = False) -> str:
 
     with ThreadPoolExecutor(max_workers=min(8, len(srcs))) as ex:
         objs = list(ex.map(compile_one, srcs))
-    r = subprocess.run([nvcc, "-shared", "-o", LIB, *objs, "-lcudart"], capture_output=True, text=True)
+    r = subprocess.run([nvcc, "-shared", "-o", lib, *objs, "-lcudart"], capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
     with open(stamp, "w") as fh:
         fh.write(sha + "\n")
-    return LIB
+    return lib
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv, profile="--profile" in sys.argv))

@@ -324,6 +324,16 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   if (warp == 5) tmem_dealloc(tmem, C::kTmemCols);
 }
 
+#ifdef DM_PROFILE
+// Tuning build only (-DDM_PROFILE): cycle counters of compute warp 0 of the first CTA.
+__device__ long long g_kv_prof[16];
+#define DM_PROF_T(var) const long long var = clock64()
+#define DM_PROF_ADD(slot, a, b) prof[slot] += (b) - (a)
+#else
+#define DM_PROF_T(var)
+#define DM_PROF_ADD(slot, a, b)
+#endif
+
 // ================================================================================================ dK / dV, pipelined (D = 128)
 // One CTA per SM: G compute groups of four warps (G = 2 or 4; group g owns the query blocks [g * 4/G, (g+1) * 4/G) of
 // every tile, 32 query columns per block; thread t % 128 = key row = TMEM lane), then one TMA warp and one MMA warp.
@@ -522,6 +532,9 @@ bwd_dkdv_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     uint32_t st_ph = 0;
     const float* qs_ptr = p.qs + static_cast<size_t>(b * p.H + hk * rep) * nblk + qt0 * 4 + blk0;
     const float* dos_ptr = p.dos + static_cast<size_t>(b * p.H + hk * rep) * nblk + qt0 * 4 + blk0;
+#ifdef DM_PROFILE
+    long long prof[12] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
+#endif
     float qs_n[CH], dos_n[CH];
 #pragma unroll
     for (int c = 0; c < CH; ++c) {
@@ -552,8 +565,11 @@ bwd_dkdv_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       const float* lse_s = sVec + st * 256 + 32 * blk0;
       const float* dl_s = lse_s + 128;
       float2 pr[CH][16];
+      DM_PROF_T(t0);
       if (ok) ok = wait_warp(full + st, st_ph, abort_flag);       // lse / delta of the tile are in smem
       if (ok) ok = wait_warp(bar_s, ph, abort_flag);
+      DM_PROF_T(t1);
+      DM_PROF_ADD(0, t0, t1);
       if (ok) {
         tc_fence_after();
         uint32_t rs[CH][32];
@@ -563,6 +579,8 @@ bwd_dkdv_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         tc_fence_before();
         __syncwarp();
         if ((tid & 31) == 0) mbar_arrive(bar_sfree);
+        DM_PROF_T(t2);
+        DM_PROF_ADD(1, t1, t2);
         uint32_t w[CH][8], xv[CH];
 #pragma unroll
         for (int c = 0; c < CH; ++c) {
@@ -590,7 +608,11 @@ bwd_dkdv_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           codes32(pr[c], sb_to_inv(psb), w[c]);
           xv[c] = sb_mul(psb, scale_to_sb(dos_c[c]));
         }
+        DM_PROF_T(t3);
+        DM_PROF_ADD(2, t2, t3);
         if (it > 0) ok = wait_warp(bar_done, ph ^ 1, abort_flag);   // the previous chains have read codes and words
+        DM_PROF_T(t4);
+        DM_PROF_ADD(3, t3, t4);
         if (ok) {
 #pragma unroll
           for (int c = 0; c < CH; ++c) {
@@ -603,8 +625,13 @@ bwd_dkdv_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           __syncwarp();
           if ((tid & 31) == 0) mbar_arrive(bar_pv);
         }
+        DM_PROF_T(t5);
+        DM_PROF_ADD(4, t4, t5);
       }
+      DM_PROF_T(t6);
       if (ok) ok = wait_warp(bar_dp, ph, abort_flag);
+      DM_PROF_T(t7);
+      DM_PROF_ADD(5, t6, t7);
       if (ok) {
         tc_fence_after();
         uint32_t rd[CH][32];
@@ -614,6 +641,8 @@ bwd_dkdv_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         tc_fence_before();
         __syncwarp();
         if ((tid & 31) == 0) mbar_arrive(bar_dpfree);
+        DM_PROF_T(t8);
+        DM_PROF_ADD(6, t7, t8);
         float am0 = 0.f, am1 = 0.f;
 #pragma unroll
         for (int c = 0; c < CH; ++c) {
@@ -634,7 +663,10 @@ bwd_dkdv_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         }
         const float wm = warp_max(fmaxf(am0, am1));
         if ((tid & 31) == 0) sXch[ph * 16 + warp] = wm;
+        DM_PROF_T(t9);
+        DM_PROF_ADD(7, t8, t9);
       }
+      DM_PROF_T(t10);
       // one dS scale per (128 queries x this quadrant's 32 keys): the groups' warps of the quadrant meet here
       bar_sync(1 + quad, 32 * C::kGroups);         // reached in every iteration, also after a failed wait
       const int st_cur = st;
@@ -644,6 +676,8 @@ bwd_dkdv_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       }
       if (++qi == n_qi) qi = 0;
       (void)st_cur;
+      DM_PROF_T(t11);
+      DM_PROF_ADD(8, t10, t11);
       if (!ok) continue;
       const float* x = sXch + ph * 16 + quad;
       float am = fmaxf(x[0], x[4]);
@@ -662,7 +696,15 @@ bwd_dkdv_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       tc_fence_before();
       __syncwarp();
       if ((tid & 31) == 0) mbar_arrive(bar_pk);
+      DM_PROF_T(t12);
+      DM_PROF_ADD(9, t11, t12);
     }
+#ifdef DM_PROFILE
+    if (blockIdx.x == 0 && blockIdx.y == 0 && tid == 0) {
+      for (int i = 0; i < 12; ++i) g_kv_prof[i] = prof[i];
+      g_kv_prof[12] = n_it;
+    }
+#endif
     if (ok) ok = wait_warp(bar_done, (n_it - 1) & 1, abort_flag);
     if (!ok) {
       raise_abort(abort_flag, p.status, kStatusTimeoutCompute);
@@ -1232,6 +1274,12 @@ static cudaError_t launch_kv_t(const CUtensorMap& tq, const CUtensorMap& tk, con
   bwd_dkdv_kernel<D, DV, DK><<<grid, 192, C::kSmemBytes, stream>>>(tq, tk, tv, tdo, p);
   return cudaGetLastError();
 }
+
+#ifdef DM_PROFILE
+extern "C" int dm_prof_read_kv(long long* host16) {
+  return static_cast<int>(cudaMemcpyFromSymbol(host16, g_kv_prof, sizeof(long long) * 16));
+}
+#endif
 
 cudaError_t launch_bwd_dkdv(int D, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                             const CUtensorMap& tdo, const BwdParams& p, cudaStream_t stream) {

@@ -8,7 +8,7 @@
 // which is exact), block sums accumulated across key tiles as compensated fp32 pairs (TwoSum), folded in fp64 at the
 // end; one fp64 divide and one fp32 store per row.
 //
-// CTA = one 128-query tile of one (batch, query head), one CTA per SM.  S = Q8 K8^T and dP = dO8 V8^T run on tcgen05
+// One persistent CTA per SM; a work item is one 128-query tile of one (batch, query head).  S = Q8 K8^T and dP = dO8 V8^T run on tcgen05
 // (kind::f8f6f4) into TMEM accumulators that are double-buffered (2 x (128 + 128) columns), so the tensor pipe works on
 // key tile i+1 while the compute warps take the exponentials of tile i.  Four compute groups of four warps (warps 0-15)
 // split the 128 key columns of a tile, 32 each, i.e. one K/V scale block per group (thread t of every group = TMEM lane
@@ -24,7 +24,7 @@ template <int D>
 struct DeltaCfg {
   static constexpr int kSub = D / 128;
   static constexpr int kTileBytes = 128 * D;
-  static constexpr int kStages = (D == 128) ? 3 : 2;
+  static constexpr int kStages = (D == 128) ? 5 : 2;
   static constexpr int kTmemCols = 512;
   static constexpr int kSmemQ = 0;
   static constexpr int kSmemDo = kTileBytes;
@@ -32,10 +32,20 @@ struct DeltaCfg {
   static constexpr int kSmemV = kSmemK + kStages * kTileBytes;
   static constexpr int kGroups = 4;                                     // compute groups, 32 key columns each
   static constexpr int kThreads = kGroups * 128 + 64;
-  static constexpr int kSmemRed = kSmemV + kStages * kTileBytes;        // 3 x 128 rows x (num, den) doubles
-  static constexpr int kSmemBar = kSmemRed + 3 * 128 * 16;
+  static constexpr int kSmemRed = kSmemV + kStages * kTileBytes;        // 3 slots x 3 groups x 128 rows x (num, den) doubles
+  static constexpr int kSmemBar = kSmemRed + 3 * 3 * 128 * 16;
   static constexpr int kSmemBytes = kSmemBar + 256 + 1024;
 };
+
+// Work item = one 128-query tile of one (batch, query head).  The kernel is persistent: gridDim.x CTAs (one per SM) walk
+// the item list with stride gridDim.x.  Items are ordered by decreasing length (causal: the last query tile of every
+// head first), so the static round-robin split is balanced to within one item, and the TMA / MMA pipeline runs across
+// item boundaries: the next item's Q / dO and first key tiles are in flight while the current item's last tiles are
+// still being reduced.
+__device__ __forceinline__ void delta_item(int item, int n_qt, int bh_count, int& qt, int& bh) {
+  qt = n_qt - 1 - item / bh_count;
+  bh = item % bh_count;
+}
 
 template <int D>
 __global__ void __launch_bounds__(DeltaCfg<D>::kThreads, 1)
@@ -50,24 +60,23 @@ delta_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ C
   uint8_t* sV = smem + C::kSmemV;
   double* sRed = reinterpret_cast<double*>(smem + C::kSmemRed);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kSmemBar);
-  uint64_t* bar_q = bars + 0;
-  uint64_t* bar_s = bars + 1;      // [2] S and dP of the buffer ready (MMA commit)
-  uint64_t* bar_c = bars + 3;      // [2] every compute warp has loaded its part of the buffer (16 arrivals)
-  uint64_t* full = bars + 5;       // [kStages] K and V of the stage landed
-  uint64_t* empty = bars + 8;      // [kStages] the MMAs reading the stage are done
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 13);
+  uint64_t* bar_q = bars + 0;      // Q and dO of the item landed
+  uint64_t* bar_qfree = bars + 1;  // every MMA that reads Q / dO of the item is done
+  uint64_t* bar_s = bars + 2;      // [2] S and dP of the buffer ready (MMA commit)
+  uint64_t* bar_c = bars + 4;      // [2] every compute warp has loaded its part of the buffer (one arrival per warp)
+  uint64_t* full = bars + 6;       // [kStages] K and V of the stage landed
+  uint64_t* empty = bars + 6 + C::kStages;   // [kStages] the MMAs reading the stage are done
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 6 + 2 * C::kStages);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 7 + 2 * C::kStages);
 
   const int tid = threadIdx.x, warp = tid >> 5;
   const int n_qt = p.N / 128;
-  const int qt = n_qt - 1 - static_cast<int>(blockIdx.x);
-  const int bh = blockIdx.y;
-  const int b = bh / p.H, h = bh % p.H;
-  const int bhk = b * p.Hk + h / (p.H / p.Hk);
-  const int n_it = p.causal ? (qt + 1) : n_qt;
+  const int bh_count = p.B * p.H;
+  const int n_items = n_qt * bh_count;
 
   if (tid == 0) {
     mbar_init(bar_q, 1);
+    mbar_init(bar_qfree, 1);
     for (int s = 0; s < 2; ++s) {
       mbar_init(bar_s + s, 1);
       mbar_init(bar_c + s, C::kGroups * 4);              // one arrival per compute warp
@@ -95,26 +104,31 @@ delta_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ C
       tma_prefetch_desc(&tm_k);
       tma_prefetch_desc(&tm_v);
       tma_prefetch_desc(&tm_do);
-      mbar_expect_tx(bar_q, 2 * C::kTileBytes);
-      for (int s = 0; s < C::kSub; ++s) {
-        tma_load_2d(sQ + s * 16384, &tm_q, bar_q, s * 128, bh * p.N + qt * 128);
-        tma_load_2d(sDo + s * 16384, &tm_do, bar_q, s * 128, bh * p.N + qt * 128);
-      }
-      for (int it = 0; it < n_it; ++it) {
-        const int st = it % C::kStages;
-        if (it >= C::kStages) {
-          if (!wait_or_abort(empty + st, ((it / C::kStages) - 1) & 1, abort_flag)) {
-            raise_abort(abort_flag, p.status, kStatusTimeoutProducer);
-            break;
+      uint32_t g = 0, n_done = 0;                      // key tiles issued so far; items started so far
+      bool ok = true;
+      for (int item = blockIdx.x; ok && item < n_items; item += gridDim.x, ++n_done) {
+        int qt, bh;
+        delta_item(item, n_qt, bh_count, qt, bh);
+        const int bhk = (bh / p.H) * p.Hk + (bh % p.H) / (p.H / p.Hk);
+        const int n_it = p.causal ? (qt + 1) : n_qt;
+        if (n_done > 0 && !(ok = wait_or_abort(bar_qfree, (n_done - 1) & 1, abort_flag))) break;
+        mbar_expect_tx(bar_q, 2 * C::kTileBytes);
+        for (int s = 0; s < C::kSub; ++s) {
+          tma_load_2d(sQ + s * 16384, &tm_q, bar_q, s * 128, bh * p.N + qt * 128);
+          tma_load_2d(sDo + s * 16384, &tm_do, bar_q, s * 128, bh * p.N + qt * 128);
+        }
+        for (int it = 0; it < n_it; ++it, ++g) {
+          const uint32_t st = g % C::kStages;
+          if (g >= C::kStages && !(ok = wait_or_abort(empty + st, ((g / C::kStages) - 1) & 1, abort_flag))) break;
+          const int row = bhk * p.N + it * 128;          // key tiles in ascending order
+          mbar_expect_tx(full + st, 2 * C::kTileBytes);
+          for (int s = 0; s < C::kSub; ++s) {
+            tma_load_2d(sK + st * C::kTileBytes + s * 16384, &tm_k, full + st, s * 128, row);
+            tma_load_2d(sV + st * C::kTileBytes + s * 16384, &tm_v, full + st, s * 128, row);
           }
         }
-        const int row = bhk * p.N + it * 128;            // key tiles in ascending order
-        mbar_expect_tx(full + st, 2 * C::kTileBytes);
-        for (int s = 0; s < C::kSub; ++s) {
-          tma_load_2d(sK + st * C::kTileBytes + s * 16384, &tm_k, full + st, s * 128, row);
-          tma_load_2d(sV + st * C::kTileBytes + s * 16384, &tm_v, full + st, s * 128, row);
-        }
       }
+      if (!ok) raise_abort(abort_flag, p.status, kStatusTimeoutProducer);
     }
   } else if (warp == 17) {
     // ------------------------------------------------------------------------------------------ MMA issuer
@@ -122,27 +136,35 @@ delta_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ C
       constexpr uint32_t kIdesc = idesc_f8(128, 128, false, false);
       const uint32_t q_lo = desc_lo(smem_u32(sQ)), do_lo = desc_lo(smem_u32(sDo));
       const uint32_t k_lo0 = desc_lo(smem_u32(sK)), v_lo0 = desc_lo(smem_u32(sV));
-      bool ok = wait_or_abort(bar_q, 0, abort_flag);
-      for (int it = 0; ok && it < n_it; ++it) {
-        const int st = it % C::kStages, buf = it & 1;
-        // the accumulator pair `buf` was last used by tile it-2: wait until both compute groups have read it
-        if (it >= 2 && !(ok = wait_or_abort(bar_c + buf, ((it - 2) >> 1) & 1, abort_flag))) break;
-        if (!(ok = wait_or_abort(full + st, (it / C::kStages) & 1, abort_flag))) break;
-        tc_fence_after();
-        const uint32_t k_lo = k_lo0 + st * (C::kTileBytes >> 4), v_lo = v_lo0 + st * (C::kTileBytes >> 4);
-        const uint32_t t_s = tmem + buf * 256, t_dp = t_s + 128;
+      uint32_t g = 0, n_done = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; ok && item < n_items; item += gridDim.x, ++n_done) {
+        int qt, bh;
+        delta_item(item, n_qt, bh_count, qt, bh);
+        const int n_it = p.causal ? (qt + 1) : n_qt;
+        if (!(ok = wait_or_abort(bar_q, n_done & 1, abort_flag))) break;
+        for (int it = 0; it < n_it; ++it, ++g) {
+          const uint32_t st = g % C::kStages, buf = g & 1;
+          // the accumulator pair `buf` was last used two tiles ago: wait until every compute warp has read it
+          if (g >= 2 && !(ok = wait_or_abort(bar_c + buf, ((g - 2) >> 1) & 1, abort_flag))) break;
+          if (!(ok = wait_or_abort(full + st, (g / C::kStages) & 1, abort_flag))) break;
+          tc_fence_after();
+          const uint32_t k_lo = k_lo0 + st * (C::kTileBytes >> 4), v_lo = v_lo0 + st * (C::kTileBytes >> 4);
+          const uint32_t t_s = tmem + buf * 256, t_dp = t_s + 128;
 #pragma unroll
-        for (int ks = 0; ks < D / 32; ++ks) {
-          const uint32_t off = (ks / 4) * 1024 + (ks % 4) * 2;      // descriptor units of 16 bytes
-          mma_f8_ss(t_s, q_lo + off, k_lo + off, kIdesc, ks > 0);
-        }
+          for (int ks = 0; ks < D / 32; ++ks) {
+            const uint32_t off = (ks / 4) * 1024 + (ks % 4) * 2;      // descriptor units of 16 bytes
+            mma_f8_ss(t_s, q_lo + off, k_lo + off, kIdesc, ks > 0);
+          }
 #pragma unroll
-        for (int ks = 0; ks < D / 32; ++ks) {
-          const uint32_t off = (ks / 4) * 1024 + (ks % 4) * 2;
-          mma_f8_ss(t_dp, do_lo + off, v_lo + off, kIdesc, ks > 0);
+          for (int ks = 0; ks < D / 32; ++ks) {
+            const uint32_t off = (ks / 4) * 1024 + (ks % 4) * 2;
+            mma_f8_ss(t_dp, do_lo + off, v_lo + off, kIdesc, ks > 0);
+          }
+          tc_commit(empty + st);
+          tc_commit(bar_s + buf);
         }
-        tc_commit(empty + st);
-        tc_commit(bar_s + buf);
+        tc_commit(bar_qfree);
       }
       if (!ok) raise_abort(abort_flag, p.status, kStatusTimeoutMma);
     }
@@ -151,74 +173,84 @@ delta_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ C
     const int wg = warp >> 2;                          // key columns [32 wg, 32 wg + 32) of every tile: scale block wg
     const int r = tid & 127;                           // query row inside the tile = TMEM lane
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
-    const int row = qt * 128 + r;
     const int nblk = p.N / 32;
-    const float qs = p.qs[static_cast<size_t>(bh) * nblk + row / 32];
-    const float dos = p.dos[static_cast<size_t>(bh) * nblk + row / 32];
-    const float2 nl2 = splat2(-(p.lse[static_cast<size_t>(bh) * p.N + row] * kLog2e));
-    const float* ks_base = p.ks + static_cast<size_t>(bhk) * nblk + wg;
-    const float* vs_base = p.vs + static_cast<size_t>(bhk) * nblk + wg;
-    float ks1 = *ks_base, vs1 = *vs_base;
-    // running sums as unevaluated fp32 pairs (hi + lo, TwoSum): exact to ~2^-48 relative without touching the fp64 pipe
-    float num_hi = 0.f, num_lo = 0.f, den_hi = 0.f, den_lo = 0.f;
+    uint32_t g = 0, n_done = 0;
     bool ok = true;
-    for (int it = 0; it < n_it; ++it) {
-      const int buf = it & 1;
-      const float2 c2 = splat2((ks1 * qs) * kLog2e);
-      // a = vs * dos is a power of two, so P * (dP_acc * a) == (P * dP_acc) * a exactly: a is applied once per block
-      const float a = vs1 * dos;
-      if (it + 1 < n_it) {                             // scales of the next key tile, in flight during this one
-        ks1 = ks_base[(it + 1) * 4];
-        vs1 = vs_base[(it + 1) * 4];
-      }
-      const bool diag = p.causal && (it == qt);
-      if (!(ok = wait_warp(bar_s + buf, (it >> 1) & 1, abort_flag))) break;
-      tc_fence_after();
-      uint32_t s[32], dp[32];
-      tmem_ld32(tmem + lane_base + buf * 256 + 32 * wg, s);
-      tmem_ld32(tmem + lane_base + buf * 256 + 128 + 32 * wg, dp);
-      tmem_wait_ld();
-      tc_fence_before();
-      __syncwarp();
-      if ((tid & 31) == 0) mbar_arrive(bar_c + buf);   // this warp's part of the buffer is in registers: hand it back
-      if (diag) {
+    for (int item = blockIdx.x; item < n_items; item += gridDim.x, ++n_done) {
+      int qt, bh;
+      delta_item(item, n_qt, bh_count, qt, bh);
+      const int bhk = (bh / p.H) * p.Hk + (bh % p.H) / (p.H / p.Hk);
+      const int n_it = p.causal ? (qt + 1) : n_qt;
+      const int row = qt * 128 + r;
+      const float qs = p.qs[static_cast<size_t>(bh) * nblk + row / 32];
+      const float dos = p.dos[static_cast<size_t>(bh) * nblk + row / 32];
+      const float2 nl2 = splat2(-(p.lse[static_cast<size_t>(bh) * p.N + row] * kLog2e));
+      const float* ks_base = p.ks + static_cast<size_t>(bhk) * nblk + wg;
+      const float* vs_base = p.vs + static_cast<size_t>(bhk) * nblk + wg;
+      float ks1 = *ks_base, vs1 = *vs_base;
+      // running sums as unevaluated fp32 pairs (hi + lo, TwoSum): exact to ~2^-48 relative without the fp64 pipe
+      float num_hi = 0.f, num_lo = 0.f, den_hi = 0.f, den_lo = 0.f;
+      for (int it = 0; ok && it < n_it; ++it, ++g) {
+        const uint32_t buf = g & 1;
+        const float2 c2 = splat2((ks1 * qs) * kLog2e);
+        // a = vs * dos is a power of two, so P * (dP_acc * a) == (P * dP_acc) * a exactly: a is applied once per block
+        const float a = vs1 * dos;
+        if (it + 1 < n_it) {                           // scales of the next key tile, in flight during this one
+          ks1 = ks_base[(it + 1) * 4];
+          vs1 = vs_base[(it + 1) * 4];
+        }
+        const bool diag = p.causal && (it == qt);
+        if (!(ok = wait_warp(bar_s + buf, (g >> 1) & 1, abort_flag))) break;
+        tc_fence_after();
+        uint32_t s[32], dp[32];
+        tmem_ld32(tmem + lane_base + buf * 256 + 32 * wg, s);
+        tmem_ld32(tmem + lane_base + buf * 256 + 128 + 32 * wg, dp);
+        tmem_wait_ld();
+        tc_fence_before();
+        __syncwarp();
+        if ((tid & 31) == 0) mbar_arrive(bar_c + buf);   // this warp's part of the buffer is in registers: hand it back
+        if (diag) {
 #pragma unroll
-        for (int e = 0; e < 32; ++e)
-          if (32 * wg + e > r) s[e] = 0xff800000u;     // -inf: key index above the query index
-      }
-      float2 n0 = make_float2(0.f, 0.f), n1 = n0, d0 = n0, d1 = n0;
+          for (int e = 0; e < 32; ++e)
+            if (32 * wg + e > r) s[e] = 0xff800000u;     // -inf: key index above the query index
+        }
+        float2 n0 = make_float2(0.f, 0.f), n1 = n0, d0 = n0, d1 = n0;
 #pragma unroll
-      for (int e = 0; e < 16; e += 2) {
-        const float2 p0 = ex2_2(fma2(make_float2(__uint_as_float(s[2 * e]), __uint_as_float(s[2 * e + 1])), c2, nl2));
-        const float2 p1 = ex2_2(fma2(make_float2(__uint_as_float(s[2 * e + 2]), __uint_as_float(s[2 * e + 3])), c2, nl2));
-        n0 = fma2(p0, make_float2(__uint_as_float(dp[2 * e]), __uint_as_float(dp[2 * e + 1])), n0);
-        n1 = fma2(p1, make_float2(__uint_as_float(dp[2 * e + 2]), __uint_as_float(dp[2 * e + 3])), n1);
-        d0 = add2(d0, p0);
-        d1 = add2(d1, p1);
+        for (int e = 0; e < 16; e += 2) {
+          const float2 p0 = ex2_2(fma2(make_float2(__uint_as_float(s[2 * e]), __uint_as_float(s[2 * e + 1])), c2, nl2));
+          const float2 p1 = ex2_2(fma2(make_float2(__uint_as_float(s[2 * e + 2]), __uint_as_float(s[2 * e + 3])), c2, nl2));
+          n0 = fma2(p0, make_float2(__uint_as_float(dp[2 * e]), __uint_as_float(dp[2 * e + 1])), n0);
+          n1 = fma2(p1, make_float2(__uint_as_float(dp[2 * e + 2]), __uint_as_float(dp[2 * e + 3])), n1);
+          d0 = add2(d0, p0);
+          d1 = add2(d1, p1);
+        }
+        const float nb = ((n0.x + n0.y) + (n1.x + n1.y)) * a;
+        const float db = (d0.x + d0.y) + (d1.x + d1.y);
+        two_sum_acc(num_hi, num_lo, nb);
+        two_sum_acc(den_hi, den_lo, db);
       }
-      const float nb = ((n0.x + n0.y) + (n1.x + n1.y)) * a;
-      const float db = (d0.x + d0.y) + (d1.x + d1.y);
-      two_sum_acc(num_hi, num_lo, nb);
-      two_sum_acc(den_hi, den_lo, db);
+      // fold the groups' partial sums in fp64: groups 1-3 publish, group 0 adds in group order and stores.  Slots and
+      // named barriers rotate over three items: a warp can run at most two tiles, hence two items, ahead of another.
+      const int slot = n_done % 3;
+      double* red = sRed + slot * (3 * 128 * 2);
+      const double num = static_cast<double>(num_hi) + static_cast<double>(num_lo);
+      const double den = static_cast<double>(den_hi) + static_cast<double>(den_lo);
+      if (wg > 0) {
+        red[((wg - 1) * 128 + r) * 2] = num;
+        red[((wg - 1) * 128 + r) * 2 + 1] = den;
+        bar_arrive(1 + slot, C::kGroups * 128);
+      } else {
+        bar_sync(1 + slot, C::kGroups * 128);
+        double n = num, dd = den;
+#pragma unroll
+        for (int gi = 0; gi < C::kGroups - 1; ++gi) {
+          n += red[(gi * 128 + r) * 2];
+          dd += red[(gi * 128 + r) * 2 + 1];
+        }
+        if (ok) p.delta[static_cast<size_t>(bh) * p.N + row] = static_cast<float>(n / dd);
+      }
     }
     if (!ok) raise_abort(abort_flag, p.status, kStatusTimeoutCompute);
-    // fold the groups' partial sums in fp64: groups 1-3 publish, group 0 adds in group order and stores
-    const double num = static_cast<double>(num_hi) + static_cast<double>(num_lo);
-    const double den = static_cast<double>(den_hi) + static_cast<double>(den_lo);
-    if (wg > 0) {
-      sRed[((wg - 1) * 128 + r) * 2] = num;
-      sRed[((wg - 1) * 128 + r) * 2 + 1] = den;
-      bar_arrive(1, C::kGroups * 128);
-    } else {
-      bar_sync(1, C::kGroups * 128);
-      double n = num, dd = den;
-#pragma unroll
-      for (int g = 0; g < C::kGroups - 1; ++g) {
-        n += sRed[(g * 128 + r) * 2];
-        dd += sRed[(g * 128 + r) * 2 + 1];
-      }
-      if (ok) p.delta[static_cast<size_t>(bh) * p.N + row] = static_cast<float>(n / dd);
-    }
   }
   tc_fence_before();
   __syncthreads();
@@ -237,8 +269,14 @@ static cudaError_t launch_delta_t(const CUtensorMap& tq, const CUtensorMap& tk, 
     if (e != cudaSuccess) return e;
     attr_set[dev] = true;
   }
-  dim3 grid(p.N / 128, p.B * p.H);
-  delta_kernel<D><<<grid, C::kThreads, C::kSmemBytes, stream>>>(tq, tk, tv, tdo, p);
+  static int sm_count[64] = {};
+  if (dev >= 0 && dev < 64 && sm_count[dev] == 0) {
+    cudaError_t e = cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) return e;
+  }
+  const int n_items = (p.N / 128) * p.B * p.H;
+  const int ctas = (dev >= 0 && dev < 64) ? sm_count[dev] : 148;
+  delta_kernel<D><<<n_items < ctas ? n_items : ctas, C::kThreads, C::kSmemBytes, stream>>>(tq, tk, tv, tdo, p);
   return cudaGetLastError();
 }
 

@@ -61,7 +61,15 @@ __global__ void kmean_fold_kernel(const KMeanParams p) {
   for (int c = threadIdx.x; c < p.D; c += blockDim.x) {
     const float* src = p.partial + static_cast<size_t>(bh) * nchunk * p.D + c;
     float s = 0.f;
-    for (int j = 0; j < nchunk; ++j) s += src[static_cast<size_t>(j) * p.D];
+    int j = 0;
+    for (; j + 8 <= nchunk; j += 8) {               // eight loads in flight, added in chunk order
+      float v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) v[u] = src[static_cast<size_t>(j + u) * p.D];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) s += v[u];
+    }
+    for (; j < nchunk; ++j) s += src[static_cast<size_t>(j) * p.D];
     p.mean[static_cast<size_t>(bh) * p.D + c] = s / static_cast<float>(p.N);
   }
 }
