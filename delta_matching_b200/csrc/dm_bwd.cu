@@ -992,7 +992,7 @@ bwd_dq_serial_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
 // own, and dQ += dS K runs behind the next tile's compute.
 struct DqCfg {
   static constexpr int kTileBytes = 128 * 128;
-  static constexpr int kStages = 3;
+  static constexpr int kStages = 4;
   static constexpr int kGroups = 4;
   static constexpr int kThreads = kGroups * 128 + 64;
   static constexpr int kTmemCols = 512;
@@ -1005,10 +1005,23 @@ struct DqCfg {
   static constexpr int kSmemV = kSmemK + kStages * kTileBytes;
   static constexpr int kSmemDs = kSmemV + kStages * kTileBytes;      // 2 x (128 x 128 dS codes, rows = queries)
   static constexpr int kSmemRed = kSmemDs + 2 * kTileBytes;          // 2 x [16 warps] block maxima, then probe sums
-  static constexpr int kSmemProbe = kSmemRed + 2 * 16 * 4;           // 3 groups x 128 rows x 2 doubles
-  static constexpr int kSmemBar = kSmemProbe + 3 * 128 * 16;
+  static constexpr int kSmemProbe = kSmemRed + 2 * 16 * 4;           // 3 slots x 3 groups x 128 rows x 2 doubles
+  static constexpr int kSmemBar = kSmemProbe + 3 * 3 * 128 * 16;
   static constexpr int kSmemBytes = kSmemBar + 256 + 1024;
 };
+
+// Work item = one 128-query tile of one (batch, query head); persistent CTAs (one per SM) walk the item list with stride
+// gridDim.x, heaviest items first, and the TMA / MMA pipeline runs across item boundaries.
+struct DqWalk {                      // position of a role in the CTA's sequence of (item, key tile) pairs
+  int item, it, n_it, qt, bh;
+  uint32_t n_done;                   // items finished before the current one
+};
+__device__ __forceinline__ void dq_walk_set(DqWalk& w, const BwdParams& p, int n_t, int bh_count) {
+  w.qt = n_t - 1 - w.item / bh_count;
+  w.bh = w.item % bh_count;
+  w.n_it = p.causal ? (w.qt + 1) : n_t;
+  w.it = 0;
+}
 
 __global__ void __launch_bounds__(DqCfg::kThreads, 1)
 bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
@@ -1024,30 +1037,31 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   float* sRed = reinterpret_cast<float*>(smem + C::kSmemRed);
   double* sProbe = reinterpret_cast<double*>(smem + C::kSmemProbe);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kSmemBar);
-  uint64_t* bar_q = bars + 0;
-  uint64_t* bar_s = bars + 1;        // S and dP of the tile ready (MMA commit)
-  uint64_t* bar_free = bars + 2;     // every compute warp holds its part of the tile in registers (16 arrivals)
-  uint64_t* bar_p = bars + 3;        // dS codes and scale words written (16 arrivals)
-  uint64_t* bar_done = bars + 4;     // dQ chain of the tile done (MMA commit)
-  uint64_t* full = bars + 5;         // [kStages]
-  uint64_t* empty = bars + 8;        // [kStages]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 13);
+  uint64_t* bar_q = bars + 0;        // Q and dO of the item landed
+  uint64_t* bar_qfree = bars + 1;    // every MMA that reads Q / dO of the item is done
+  uint64_t* bar_s = bars + 2;        // S and dP of the tile ready (MMA commit)
+  uint64_t* bar_free = bars + 3;     // every compute warp holds its part of the tile in registers (16 arrivals)
+  uint64_t* bar_p = bars + 4;        // dS codes and scale words written (16 arrivals)
+  uint64_t* bar_done = bars + 5;     // dQ chain of the tile done (MMA commit)
+  uint64_t* bar_dqfree = bars + 6;   // the item's dQ accumulator has been read out (16 arrivals)
+  uint64_t* full = bars + 7;         // [kStages]
+  uint64_t* empty = bars + 7 + C::kStages;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 7 + 2 * C::kStages);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 8 + 2 * C::kStages);
 
   const int tid = threadIdx.x, warp = tid >> 5;
   const int n_t = p.N / 128;
-  const int qt = n_t - 1 - static_cast<int>(blockIdx.x);
-  const int bh = blockIdx.y;
-  const int b = bh / p.H, h = bh % p.H;
-  const int bhk = b * p.Hk + h / (p.H / p.Hk);
-  const int n_it = p.causal ? (qt + 1) : n_t;
+  const int bh_count = p.B * p.H;
+  const int n_items = n_t * bh_count;
 
   if (tid == 0) {
     mbar_init(bar_q, 1);
+    mbar_init(bar_qfree, 1);
     mbar_init(bar_s, 1);
     mbar_init(bar_free, C::kGroups * 4);
     mbar_init(bar_p, C::kGroups * 4);
     mbar_init(bar_done, 1);
+    mbar_init(bar_dqfree, C::kGroups * 4);
     for (int s = 0; s < C::kStages; ++s) {
       mbar_init(full + s, 1);
       mbar_init(empty + s, 1);
@@ -1071,22 +1085,26 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       tma_prefetch_desc(&tm_k);
       tma_prefetch_desc(&tm_v);
       tma_prefetch_desc(&tm_do);
-      mbar_expect_tx(bar_q, 2 * C::kTileBytes);
-      tma_load_2d(sQ, &tm_q, bar_q, 0, bh * p.N + qt * 128);
-      tma_load_2d(sDo, &tm_do, bar_q, 0, bh * p.N + qt * 128);
-      for (int it = 0; it < n_it; ++it) {
-        const int st = it % C::kStages;
-        if (it >= C::kStages) {
-          if (!wait_or_abort(empty + st, ((it / C::kStages) - 1) & 1, abort_flag)) {
-            raise_abort(abort_flag, p.status, kStatusTimeoutProducer);
-            break;
-          }
+      uint32_t g = 0, n_done = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; ok && item < n_items; item += gridDim.x, ++n_done) {
+        const int qt = n_t - 1 - item / bh_count, bh = item % bh_count;
+        const int bhk = (bh / p.H) * p.Hk + (bh % p.H) / (p.H / p.Hk);
+        const int n_it = p.causal ? (qt + 1) : n_t;
+        if (n_done > 0 && !(ok = wait_or_abort(bar_qfree, (n_done - 1) & 1, abort_flag))) break;
+        mbar_expect_tx(bar_q, 2 * C::kTileBytes);
+        tma_load_2d(sQ, &tm_q, bar_q, 0, bh * p.N + qt * 128);
+        tma_load_2d(sDo, &tm_do, bar_q, 0, bh * p.N + qt * 128);
+        for (int it = 0; it < n_it; ++it, ++g) {
+          const uint32_t st = g % C::kStages;
+          if (g >= C::kStages && !(ok = wait_or_abort(empty + st, ((g / C::kStages) - 1) & 1, abort_flag))) break;
+          const int row = bhk * p.N + it * 128;
+          mbar_expect_tx(full + st, 2 * C::kTileBytes);
+          tma_load_2d(sK + st * C::kTileBytes, &tm_k, full + st, 0, row);
+          tma_load_2d(sV + st * C::kTileBytes, &tm_v, full + st, 0, row);
         }
-        const int row = bhk * p.N + it * 128;
-        mbar_expect_tx(full + st, 2 * C::kTileBytes);
-        tma_load_2d(sK + st * C::kTileBytes, &tm_k, full + st, 0, row);
-        tma_load_2d(sV + st * C::kTileBytes, &tm_v, full + st, 0, row);
       }
+      if (!ok) raise_abort(abort_flag, p.status, kStatusTimeoutProducer);
     }
   } else if (warp == 17) {
     // ------------------------------------------------------------------------------------------ MMA issuer
@@ -1094,39 +1112,59 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       constexpr uint32_t kIdesc = idesc_f8(128, 128, false, false);
       const uint32_t q_lo = desc_lo(smem_u32(sQ)), do_lo = desc_lo(smem_u32(sDo)), ds_lo0 = desc_lo(smem_u32(sDs));
       const uint32_t k_lo0 = desc_lo(smem_u32(sK)), v_lo0 = desc_lo(smem_u32(sV));
-      auto issue_s_dp = [&](int st) {
+      bool ok = true;
+      // `nx` runs one tile ahead of `cur`: S / dP of the next tile (possibly the first tile of the next item) are
+      // issued as soon as the compute warps hold the current tile in registers.
+      DqWalk cur{static_cast<int>(blockIdx.x), 0, 0, 0, 0, 0}, nx = cur;
+      uint32_t g_nx = 0;                                // tiles whose S / dP have been issued
+      auto issue_s_dp = [&]() -> bool {                 // for the tile `nx` points at; advances nx
+        if (nx.it == 0 && !wait_or_abort(bar_q, nx.n_done & 1, abort_flag)) return false;
+        const uint32_t st = g_nx % C::kStages;
+        if (!wait_or_abort(full + st, (g_nx / C::kStages) & 1, abort_flag)) return false;
+        tc_fence_after();
         const uint32_t k_lo = k_lo0 + st * (C::kTileBytes >> 4), v_lo = v_lo0 + st * (C::kTileBytes >> 4);
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks) mma_f8_ss(tmem + C::kColS, q_lo + ks * 2, k_lo + ks * 2, kIdesc, ks > 0);
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks) mma_f8_ss(tmem + C::kColDp, do_lo + ks * 2, v_lo + ks * 2, kIdesc, ks > 0);
         tc_commit(bar_s);
-      };
-      bool ok = wait_or_abort(bar_q, 0, abort_flag);
-      if (ok) ok = wait_or_abort(full + 0, 0, abort_flag);
-      if (ok) {
-        tc_fence_after();
-        issue_s_dp(0);
-      }
-      for (int it = 0; ok && it < n_it; ++it) {
-        const int st = it % C::kStages;
-        if (!(ok = wait_or_abort(bar_free, it & 1, abort_flag))) break;
-        if (it + 1 < n_it) {
-          const int sn = (it + 1) % C::kStages;
-          if (!(ok = wait_or_abort(full + sn, ((it + 1) / C::kStages) & 1, abort_flag))) break;
-          tc_fence_after();
-          issue_s_dp(sn);
+        ++g_nx;
+        if (++nx.it == nx.n_it) {                       // last tile of the item: its Q / dO may be replaced
+          tc_commit(bar_qfree);
+          nx.item += gridDim.x;
+          ++nx.n_done;
+          if (nx.item < n_items) dq_walk_set(nx, p, n_t, bh_count);
         }
-        if (!(ok = wait_or_abort(bar_p, it & 1, abort_flag))) break;
+        return true;
+      };
+      if (cur.item < n_items) {
+        dq_walk_set(cur, p, n_t, bh_count);
+        nx = cur;
+        ok = issue_s_dp();
+      }
+      uint32_t g = 0;                                   // tiles whose dQ chain has been issued
+      while (ok && cur.item < n_items) {
+        const uint32_t st = g % C::kStages;
+        if (!(ok = wait_or_abort(bar_free, g & 1, abort_flag))) break;
+        if (nx.item < n_items && !(ok = issue_s_dp())) break;
+        if (!(ok = wait_or_abort(bar_p, g & 1, abort_flag))) break;
+        // the first chain of an item overwrites the accumulator: the previous item's dQ must have been read out
+        if (cur.it == 0 && cur.n_done > 0 && !(ok = wait_or_abort(bar_dqfree, (cur.n_done - 1) & 1, abort_flag))) break;
         tc_fence_after();
         // dQ += dS K: A = dS codes in shared memory (rows = queries, K-major), B = K tile MN-major (32 key rows per step)
-        const uint32_t ds_lo = ds_lo0 + (it & 1) * (C::kTileBytes >> 4), k_lo = k_lo0 + st * (C::kTileBytes >> 4);
+        const uint32_t ds_lo = ds_lo0 + (g & 1) * (C::kTileBytes >> 4), k_lo = k_lo0 + st * (C::kTileBytes >> 4);
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks)
           mma_mxf8_ss(tmem + C::kColDq, ds_lo + ks * 2, k_lo + ks * 256, idesc_mxf8(128, 128, false, true, 0, 0),
-                      tmem + C::kColX + 4 * ks, tmem + C::kColOne, (it > 0) || (ks > 0));
+                      tmem + C::kColX + 4 * ks, tmem + C::kColOne, (cur.it > 0) || (ks > 0));
         tc_commit(empty + st);
         tc_commit(bar_done);
+        ++g;
+        if (++cur.it == cur.n_it) {
+          cur.item += gridDim.x;
+          ++cur.n_done;
+          if (cur.item < n_items) dq_walk_set(cur, p, n_t, bh_count);
+        }
       }
       if (!ok) raise_abort(abort_flag, p.status, kStatusTimeoutMma);
     }
@@ -1135,115 +1173,128 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     const int wg = warp >> 2;
     const int r = tid & 127;
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
-    const int row = qt * 128 + r;
     const int nblk = p.N / 32;
-    const float qs = p.qs[static_cast<size_t>(bh) * nblk + row / 32];
-    const float dos = p.dos[static_cast<size_t>(bh) * nblk + row / 32];
-    const float2 nl2 = splat2(-(p.lse[static_cast<size_t>(bh) * p.N + row] * kLog2e));
-    const float2 ndl = splat2(-p.delta[static_cast<size_t>(bh) * p.N + row]);
     const bool probe = p.rowsum_ds != nullptr;
-    const float* ks_base = p.ks + static_cast<size_t>(bhk) * nblk + wg;
-    const float* vs_base = p.vs + static_cast<size_t>(bhk) * nblk + wg;
-    float ks1 = *ks_base, vs1 = *vs_base;
-    double rs_acc = 0.0, ap_acc = 0.0;
+    uint32_t g = 0, n_done = 0;
     bool ok = true;
-    for (int it = 0; it < n_it; ++it) {
-      const float ksv = ks1, vsv = vs1;
-      if (it + 1 < n_it) {
-        ks1 = ks_base[(it + 1) * 4];
-        vs1 = vs_base[(it + 1) * 4];
+    for (int item = blockIdx.x; item < n_items; item += gridDim.x, ++n_done) {
+      const int qt = n_t - 1 - item / bh_count, bh = item % bh_count;
+      const int b = bh / p.H, h = bh % p.H;
+      const int bhk = b * p.Hk + h / (p.H / p.Hk);
+      const int n_it = p.causal ? (qt + 1) : n_t;
+      const int row = qt * 128 + r;
+      const float qs = p.qs[static_cast<size_t>(bh) * nblk + row / 32];
+      const float dos = p.dos[static_cast<size_t>(bh) * nblk + row / 32];
+      const float2 nl2 = splat2(-(p.lse[static_cast<size_t>(bh) * p.N + row] * kLog2e));
+      const float2 ndl = splat2(-p.delta[static_cast<size_t>(bh) * p.N + row]);
+      const float* ks_base = p.ks + static_cast<size_t>(bhk) * nblk + wg;
+      const float* vs_base = p.vs + static_cast<size_t>(bhk) * nblk + wg;
+      float ks1 = *ks_base, vs1 = *vs_base;
+      double rs_acc = 0.0, ap_acc = 0.0;
+      for (int it = 0; it < n_it; ++it, ++g) {
+        const float ksv = ks1, vsv = vs1;
+        if (it + 1 < n_it) {
+          ks1 = ks_base[(it + 1) * 4];
+          vs1 = vs_base[(it + 1) * 4];
+        }
+        const bool diag = p.causal && (it == qt);
+        float2 v[16];
+        if (ok) ok = wait_warp(bar_s, g & 1, abort_flag);
+        if (ok) {
+          tc_fence_after();
+          uint32_t rs[32], rd[32];
+          tmem_ld32(tmem + lane_base + C::kColS + 32 * wg, rs);
+          tmem_ld32(tmem + lane_base + C::kColDp + 32 * wg, rd);
+          tmem_wait_ld();
+          tc_fence_before();
+          __syncwarp();
+          if ((tid & 31) == 0) mbar_arrive(bar_free);    // this warp's part of the accumulators may be overwritten now
+          if (diag) {
+#pragma unroll
+            for (int e = 0; e < 32; ++e)
+              if (32 * wg + e > r) rs[e] = 0xff800000u;  // -inf: key index above the query index
+          }
+          const float2 cc = splat2((ksv * qs) * kLog2e), aa = splat2(vsv * dos);
+          float am0 = 0.f, am1 = 0.f;
+          float2 rsum = make_float2(0.f, 0.f), asum = rsum;
+#pragma unroll
+          for (int e = 0; e < 16; ++e) {
+            const float2 pe = ex2_2(fma2(make_float2(__uint_as_float(rs[2 * e]), __uint_as_float(rs[2 * e + 1])), cc, nl2));
+            const float2 dp = make_float2(__uint_as_float(rd[2 * e]), __uint_as_float(rd[2 * e + 1]));
+            const float2 t = fma2(dp, aa, ndl);          // dP_acc * a - delta: a is a power of two, the product is exact
+            const float2 d = mul2(pe, t);
+            v[e] = d;
+            if (e & 1) am1 = max3(am1, fabsf(d.x), fabsf(d.y));
+            else am0 = max3(am0, fabsf(d.x), fabsf(d.y));
+            if (probe) {
+              rsum = add2(rsum, d);
+              const float2 pd = mul2(pe, mul2(dp, aa));
+              asum = add2(asum, make_float2(fabsf(pd.x), fabsf(pd.y)));
+            }
+          }
+          if (probe) {
+            rs_acc += static_cast<double>(rsum.x) + static_cast<double>(rsum.y);
+            ap_acc += static_cast<double>(asum.x) + static_cast<double>(asum.y);
+          }
+          // one scale per (128 queries x 32 keys): the maxima of this group's four warps meet in shared memory
+          const float wm = warp_max(fmaxf(am0, am1));
+          if ((tid & 31) == 0) sRed[(g & 1) * 16 + warp] = wm;
+        }
+        bar_sync(1 + wg, 128);        // reached by every warp of the group in every iteration, also after a failed wait
+        if (ok && g > 0) ok = wait_warp(bar_done, (g - 1) & 1, abort_flag);   // the previous chain has read its scale words
+        if (!ok) continue;
+        const float* red = sRed + (g & 1) * 16 + wg * 4;
+        const uint32_t dsb = pow2_sb(fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3])), 127u);
+        uint32_t w[8];
+        codes32(v, sb_to_inv(dsb), w);
+        // row r of the dS tile: 16-byte chunk j of the row lands at chunk (j ^ (r % 8)) (128-byte swizzle)
+        uint8_t* ds_row = sDs + (g & 1) * C::kTileBytes + r * 128;
+        *reinterpret_cast<uint4*>(ds_row + (((2 * wg) ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+        *reinterpret_cast<uint4*>(ds_row + (((2 * wg + 1) ^ (r & 7)) << 4)) = make_uint4(w[4], w[5], w[6], w[7]);
+        const uint32_t word = sb_mul(dsb, scale_to_sb(ksv));
+        tmem_st4(tmem + lane_base + C::kColX + 4 * wg, word, word, word, word);
+        if (wg == 0) tmem_st4(tmem + lane_base + C::kColOne, 0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu);
+        tmem_wait_st();
+        fence_async_smem();
+        tc_fence_before();
+        __syncwarp();
+        if ((tid & 31) == 0) mbar_arrive(bar_p);
       }
-      const bool diag = p.causal && (it == qt);
-      float2 v[16];
-      if (ok) ok = wait_warp(bar_s, it & 1, abort_flag);
+      // item epilogue: dQ of the item out of TMEM, then hand the accumulator to the next item
+      if (ok) ok = wait_warp(bar_done, (g - 1) & 1, abort_flag);
       if (ok) {
         tc_fence_after();
-        uint32_t rs[32], rd[32];
-        tmem_ld32(tmem + lane_base + C::kColS + 32 * wg, rs);
-        tmem_ld32(tmem + lane_base + C::kColDp + 32 * wg, rd);
+        __nv_bfloat16* dst = p.dq + static_cast<int64_t>(b) * p.dq_sb + static_cast<int64_t>(row) * p.dq_sn +
+                             static_cast<int64_t>(h) * p.dq_sh + 32 * wg;
+        uint32_t rr[32];
+        tmem_ld32(tmem + lane_base + C::kColDq + 32 * wg, rr);
         tmem_wait_ld();
         tc_fence_before();
         __syncwarp();
-        if ((tid & 31) == 0) mbar_arrive(bar_free);    // this warp's part of the accumulators may be overwritten now
-        if (diag) {
-#pragma unroll
-          for (int e = 0; e < 32; ++e)
-            if (32 * wg + e > r) rs[e] = 0xff800000u;  // -inf: key index above the query index
-        }
-        const float2 cc = splat2((ksv * qs) * kLog2e), aa = splat2(vsv * dos);
-        float am0 = 0.f, am1 = 0.f;
-        float2 rsum = make_float2(0.f, 0.f), asum = rsum;
-#pragma unroll
-        for (int e = 0; e < 16; ++e) {
-          const float2 pe = ex2_2(fma2(make_float2(__uint_as_float(rs[2 * e]), __uint_as_float(rs[2 * e + 1])), cc, nl2));
-          const float2 dp = make_float2(__uint_as_float(rd[2 * e]), __uint_as_float(rd[2 * e + 1]));
-          const float2 t = fma2(dp, aa, ndl);          // dP_acc * a - delta: a is a power of two, the product is exact
-          const float2 d = mul2(pe, t);
-          v[e] = d;
-          if (e & 1) am1 = max3(am1, fabsf(d.x), fabsf(d.y));
-          else am0 = max3(am0, fabsf(d.x), fabsf(d.y));
-          if (probe) {
-            rsum = add2(rsum, d);
-            const float2 pd = mul2(pe, mul2(dp, aa));
-            asum = add2(asum, make_float2(fabsf(pd.x), fabsf(pd.y)));
+        if ((tid & 31) == 0) mbar_arrive(bar_dqfree);
+        store_bf16_chunk(rr, p.sm_scale, dst);
+      }
+      if (probe) {                     // identity probe: the groups' partial row sums meet in shared memory
+        const int slot = n_done % 3;   // slots and barriers rotate: a warp is at most two items ahead of another
+        double* pr = sProbe + slot * (3 * 128 * 2);
+        if (wg > 0) {
+          pr[((wg - 1) * 128 + r) * 2] = rs_acc;
+          pr[((wg - 1) * 128 + r) * 2 + 1] = ap_acc;
+          bar_arrive(5 + slot, C::kGroups * 128);
+        } else {
+          bar_sync(5 + slot, C::kGroups * 128);
+          for (int gi = 0; gi < C::kGroups - 1; ++gi) {
+            rs_acc += pr[(gi * 128 + r) * 2];
+            ap_acc += pr[(gi * 128 + r) * 2 + 1];
+          }
+          if (ok) {
+            p.rowsum_ds[static_cast<size_t>(bh) * p.N + row] = static_cast<float>(rs_acc);
+            p.sum_abs_pdp[static_cast<size_t>(bh) * p.N + row] = static_cast<float>(ap_acc);
           }
         }
-        if (probe) {
-          rs_acc += static_cast<double>(rsum.x) + static_cast<double>(rsum.y);
-          ap_acc += static_cast<double>(asum.x) + static_cast<double>(asum.y);
-        }
-        // one scale per (128 queries x 32 keys): the maxima of this group's four warps meet in shared memory
-        const float wm = warp_max(fmaxf(am0, am1));
-        if ((tid & 31) == 0) sRed[(it & 1) * 16 + warp] = wm;
       }
-      bar_sync(1 + wg, 128);          // reached by every warp of the group in every iteration, also after a failed wait
-      if (ok && it > 0) ok = wait_warp(bar_done, (it - 1) & 1, abort_flag);   // the previous chain has read its scale words
-      if (!ok) continue;
-      const float* red = sRed + (it & 1) * 16 + wg * 4;
-      const uint32_t dsb = pow2_sb(fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3])), 127u);
-      uint32_t w[8];
-      codes32(v, sb_to_inv(dsb), w);
-      // row r of the dS tile: 16-byte chunk j of the row lands at chunk (j ^ (r % 8)) (128-byte swizzle)
-      uint8_t* ds_row = sDs + (it & 1) * C::kTileBytes + r * 128;
-      *reinterpret_cast<uint4*>(ds_row + (((2 * wg) ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
-      *reinterpret_cast<uint4*>(ds_row + (((2 * wg + 1) ^ (r & 7)) << 4)) = make_uint4(w[4], w[5], w[6], w[7]);
-      const uint32_t word = sb_mul(dsb, scale_to_sb(ksv));
-      tmem_st4(tmem + lane_base + C::kColX + 4 * wg, word, word, word, word);
-      if (wg == 0) tmem_st4(tmem + lane_base + C::kColOne, 0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu);
-      tmem_wait_st();
-      fence_async_smem();
-      tc_fence_before();
-      __syncwarp();
-      if ((tid & 31) == 0) mbar_arrive(bar_p);
     }
-    if (ok) ok = wait_warp(bar_done, (n_it - 1) & 1, abort_flag);
     if (!ok) raise_abort(abort_flag, p.status, kStatusTimeoutCompute);
-    if (ok) {
-      tc_fence_after();
-      __nv_bfloat16* dst = p.dq + static_cast<int64_t>(b) * p.dq_sb + static_cast<int64_t>(row) * p.dq_sn +
-                           static_cast<int64_t>(h) * p.dq_sh + 32 * wg;
-      uint32_t rr[32];
-      tmem_ld32(tmem + lane_base + C::kColDq + 32 * wg, rr);
-      tmem_wait_ld();
-      store_bf16_chunk(rr, p.sm_scale, dst);
-    }
-    if (probe) {                       // identity probe: the groups' partial row sums meet in shared memory
-      if (wg > 0) {
-        sProbe[((wg - 1) * 128 + r) * 2] = rs_acc;
-        sProbe[((wg - 1) * 128 + r) * 2 + 1] = ap_acc;
-        bar_arrive(5, C::kGroups * 128);
-      } else {
-        bar_sync(5, C::kGroups * 128);
-        for (int g = 0; g < C::kGroups - 1; ++g) {
-          rs_acc += sProbe[(g * 128 + r) * 2];
-          ap_acc += sProbe[(g * 128 + r) * 2 + 1];
-        }
-        if (ok) {
-          p.rowsum_ds[static_cast<size_t>(bh) * p.N + row] = static_cast<float>(rs_acc);
-          p.sum_abs_pdp[static_cast<size_t>(bh) * p.N + row] = static_cast<float>(ap_acc);
-        }
-      }
-    }
   }
   tc_fence_before();
   __syncthreads();
@@ -1330,8 +1381,11 @@ cudaError_t launch_bwd_dq(int D, const CUtensorMap& tq, const CUtensorMap& tk, c
   static bool done[64] = {};
   cudaError_t e = set_smem(bwd_dq_kernel, DqCfg::kSmemBytes, done);
   if (e != cudaSuccess) return e;
-  dim3 grid(p.N / 128, p.B * p.H);
-  bwd_dq_kernel<<<grid, DqCfg::kThreads, DqCfg::kSmemBytes, stream>>>(tq, tk, tv, tdo, p);
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int n_items = (p.N / 128) * p.B * p.H;
+  bwd_dq_kernel<<<n_items < sms ? n_items : sms, DqCfg::kThreads, DqCfg::kSmemBytes, stream>>>(tq, tk, tv, tdo, p);
   return cudaGetLastError();
 }
 
