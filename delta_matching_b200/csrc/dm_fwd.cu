@@ -12,6 +12,7 @@
 // CTA = one 128-query tile of one (batch, query head).  Warps 0-3: softmax / epilogue (thread t owns TMEM lane t = query
 // row t).  Warp 4: TMA producer.  Warp 5: MMA issuer and TMEM owner.  Every mbarrier wait is bounded.
 #include <cstdlib>
+#include <type_traits>
 #include <cuda_bf16.h>
 #include "dm_common.cuh"
 #include "dm_kernels.h"
@@ -166,7 +167,10 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
     const float* vs_base = p.vs + static_cast<size_t>(bhk) * nblk;
     float4 ks4 = *reinterpret_cast<const float4*>(ks_base + kt_first * 4);
     float4 vs4 = *reinterpret_cast<const float4*>(vs_base + kt_first * 4);
-    for (int it = 0; it < n_it; ++it) {
+    // One key tile.  kDiag: the tile on the diagonal of a causal problem (always the first one visited), where keys
+    // above the query index are masked; it is a compile-time variant so that the other tiles carry no select per element.
+    auto tile = [&](int it, auto diag_tag) -> bool {
+      constexpr bool kDiag = decltype(diag_tag)::value;
       const int kt = kt_first - it;
       const float cb[4] = {qsl * ks4.x, qsl * ks4.y, qsl * ks4.z, qsl * ks4.w};
       const uint32_t sfb = pack4(scale_to_sb(vs4.x), scale_to_sb(vs4.y), scale_to_sb(vs4.z), scale_to_sb(vs4.w));
@@ -174,18 +178,17 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         ks4 = *reinterpret_cast<const float4*>(ks_base + (kt - 1) * 4);
         vs4 = *reinterpret_cast<const float4*>(vs_base + (kt - 1) * 4);
       }
-      const bool diag = p.causal && (kt == qt);
-      if (!(ok = wait_warp(bar_s, it & 1, abort_flag))) break;
+      if (!wait_warp(bar_s, it & 1, abort_flag)) return false;
       tc_fence_after();
       float bsum[4], kb[4], bmax[4];
       uint32_t r[2][32];
       tmem_ld32(tmem + lane_base + C::kColS, r[0]);
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
+        uint32_t (&rc)[32] = r[c & 1];
         tmem_wait_ld();
         if (c < 3) tmem_ld32(tmem + lane_base + C::kColS + 32 * (c + 1), r[(c + 1) & 1]);   // next chunk in flight
-        uint32_t(&rc)[32] = r[c & 1];
-        if (diag) {
+        if (kDiag) {
 #pragma unroll
           for (int e = 0; e < 32; ++e)
             if (32 * c + e > tid) rc[e] = 0xff800000u;       // -inf: key index above the query index
@@ -243,7 +246,10 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(bar_p);
-    }
+      return true;
+    };
+    ok = p.causal ? tile(0, std::true_type{}) : tile(0, std::false_type{});
+    for (int it = 1; ok && it < n_it; ++it) ok = tile(it, std::false_type{});
     if (ok) ok = wait_warp(bar_o, (n_it - 1) & 1, abort_flag);
     if (!ok) {
       raise_abort(abort_flag, p.status, kStatusTimeoutCompute);
