@@ -19,6 +19,17 @@
 
 namespace dm {
 
+#ifdef DM_PROFILE
+// Tuning build only (-DDM_PROFILE): cycle counters of softmax warp 0 of the first CTA, read back with cudaMemcpyFromSymbol.
+__device__ long long g_fwd_prof[16];
+__device__ long long g_fwd1_prof[16];   // serial kernel
+#define DM_PROF_T(var) const long long var = clock64()
+#define DM_PROF_ADD(slot, a, b) prof[slot] += (b) - (a)
+#else
+#define DM_PROF_T(var)
+#define DM_PROF_ADD(slot, a, b)
+#endif
+
 template <int D>
 struct FwdCfg {
   static constexpr int kSub = D / 128;                 // 128-byte-wide sub-tiles per operand row
@@ -37,6 +48,10 @@ struct FwdCfg {
   static constexpr int kSmemBytes = kSmemBar + 256 + 1024;   // + slack for the 1024-byte alignment of the tile base
 };
 
+// Persistent: the grid is (CTAs per SM) x (SMs); CTA j processes work items j, j + grid, ... of a list ordered by
+// decreasing number of key tiles (item -> query tile n_qt - 1 - item / (B H), head item % (B H)).  The three roles keep
+// running tile / item counters for the barrier phases, so the K / V ring, the next Q tile and the next S run ahead into
+// the following item while the softmax warps still write out O of the current one.
 template <int D>
 __global__ void __launch_bounds__(192, (D == 128) ? 2 : 1)
 fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
@@ -50,30 +65,29 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kSmemBar);
   uint64_t* bar_q = bars + 0;
   uint64_t* bar_s = bars + 1;     // S accumulator ready (MMA commit)
-  uint64_t* bar_p = bars + 2;     // P codes + scale words written (128 arrivals)
+  uint64_t* bar_p = bars + 2;     // P codes + scale words written (one arrival per softmax warp)
   uint64_t* bar_o = bars + 3;     // PV chain done (MMA commit)
   uint64_t* full_k = bars + 4;    // [kStages]
   uint64_t* full_v = bars + 6;    // [kStages]
   uint64_t* empty = bars + 8;     // [kStages] stage free again (MMA commit)
+  uint64_t* bar_qfree = bars + 10; // the item's last S chain has read Q (MMA commit)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 13);
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int n_qt = p.N / 128;
-  const int qt = n_qt - 1 - static_cast<int>(blockIdx.x);      // heavy (long-row) tiles first when causal
-  const int bh = blockIdx.y;
-  const int b = bh / p.H, h = bh % p.H;
-  const int hk = h / (p.H / p.Hk);
-  const int bhk = b * p.Hk + hk;
-  const int n_it = p.causal ? (qt + 1) : n_qt;                  // key tiles visited, highest index first
-  const int kt_first = p.causal ? qt : (n_qt - 1);
+  const int BH = p.B * p.H;
+  const int n_items = n_qt * BH;
+  const int rep = p.H / p.Hk;
+  const int first_item = static_cast<int>(blockIdx.x), item_step = static_cast<int>(gridDim.x);
 
   if (tid == 0) {
     mbar_init(bar_q, 1);
     mbar_init(bar_s, 1);
-    mbar_init(bar_p, 128);
+    mbar_init(bar_p, 4);
     mbar_init(bar_o, 1);
+    mbar_init(bar_qfree, 1);
     for (int s = 0; s < C::kStages; ++s) {
       mbar_init(full_k + s, 1);
       mbar_init(full_v + s, 1);
@@ -97,163 +111,220 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       tma_prefetch_desc(&tm_q);
       tma_prefetch_desc(&tm_k);
       tma_prefetch_desc(&tm_v);
-      mbar_expect_tx(bar_q, C::kTileBytes);
-      for (int s = 0; s < C::kSub; ++s) tma_load_2d(sQ + s * 16384, &tm_q, bar_q, s * 128, bh * p.N + qt * 128);
-      for (int it = 0; it < n_it; ++it) {
-        const int st = it % C::kStages;
-        if (it >= C::kStages) {
-          if (!wait_or_abort(empty + st, ((it / C::kStages) - 1) & 1, abort_flag)) {
-            raise_abort(abort_flag, p.status, kStatusTimeoutProducer);
-            break;
-          }
+      bool ok = true;
+      int gt = 0, ic = 0;                                 // tiles and items issued so far by this CTA
+      for (int item = first_item; ok && item < n_items; item += item_step, ++ic) {
+        const int qt = n_qt - 1 - item / BH, bh = item % BH;
+        const int bhk = (bh / p.H) * p.Hk + (bh % p.H) / rep;
+        const int n_it = p.causal ? (qt + 1) : n_qt;
+        const int kt_first = p.causal ? qt : (n_qt - 1);
+        if (ic > 0 && !(ok = wait_or_abort(bar_qfree, (ic - 1) & 1, abort_flag))) break;
+        mbar_expect_tx(bar_q, C::kTileBytes);
+        for (int s = 0; s < C::kSub; ++s) tma_load_2d(sQ + s * 16384, &tm_q, bar_q, s * 128, bh * p.N + qt * 128);
+        for (int it = 0; it < n_it; ++it, ++gt) {
+          const int st = gt % C::kStages;
+          if (gt >= C::kStages && !(ok = wait_or_abort(empty + st, ((gt / C::kStages) - 1) & 1, abort_flag))) break;
+          const int row = bhk * p.N + (kt_first - it) * 128;
+          mbar_expect_tx(full_k + st, C::kTileBytes);
+          for (int s = 0; s < C::kSub; ++s)
+            tma_load_2d(sK + st * C::kTileBytes + s * 16384, &tm_k, full_k + st, s * 128, row);
+          mbar_expect_tx(full_v + st, C::kTileBytes);
+          for (int s = 0; s < C::kSub; ++s)
+            tma_load_2d(sV + st * C::kTileBytes + s * 16384, &tm_v, full_v + st, s * 128, row);
         }
-        const int row = bhk * p.N + (kt_first - it) * 128;
-        mbar_expect_tx(full_k + st, C::kTileBytes);
-        for (int s = 0; s < C::kSub; ++s)
-          tma_load_2d(sK + st * C::kTileBytes + s * 16384, &tm_k, full_k + st, s * 128, row);
-        mbar_expect_tx(full_v + st, C::kTileBytes);
-        for (int s = 0; s < C::kSub; ++s)
-          tma_load_2d(sV + st * C::kTileBytes + s * 16384, &tm_v, full_v + st, s * 128, row);
       }
+      if (!ok) raise_abort(abort_flag, p.status, kStatusTimeoutProducer);
     }
   } else if (warp == 5) {
     // ------------------------------------------------------------------------------------------ MMA issuer
     if (elect_one()) {
       constexpr uint32_t kIdescS = idesc_f8(128, 128, false, false);
       const uint32_t q_lo = desc_lo(smem_u32(sQ)), k_lo0 = desc_lo(smem_u32(sK)), v_lo0 = desc_lo(smem_u32(sV));
-      bool ok = wait_or_abort(bar_q, 0, abort_flag);
-      for (int it = 0; ok && it < n_it; ++it) {
-        const int st = it % C::kStages;
-        const uint32_t ph = (it / C::kStages) & 1;
-        if (!(ok = wait_or_abort(full_k + st, ph, abort_flag))) break;
-        tc_fence_after();
-        // S = Q K^T: both operands K-major, k-step of 32 bytes inside the 128-byte swizzle row
-        const uint32_t k_lo = k_lo0 + st * (C::kTileBytes >> 4), v_lo = v_lo0 + st * (C::kTileBytes >> 4);
+      bool ok = true;
+      int gt = 0, ic = 0;
+      for (int item = first_item; ok && item < n_items; item += item_step, ++ic) {
+        const int qt = n_qt - 1 - item / BH;
+        const int n_it = p.causal ? (qt + 1) : n_qt;
+        if (!(ok = wait_or_abort(bar_q, ic & 1, abort_flag))) break;
+        for (int it = 0; it < n_it; ++it, ++gt) {
+          const int st = gt % C::kStages;
+          const uint32_t ph = (gt / C::kStages) & 1;
+          if (!(ok = wait_or_abort(full_k + st, ph, abort_flag))) break;
+          tc_fence_after();
+          // S = Q K^T: both operands K-major, k-step of 32 bytes inside the 128-byte swizzle row
+          const uint32_t k_lo = k_lo0 + st * (C::kTileBytes >> 4), v_lo = v_lo0 + st * (C::kTileBytes >> 4);
 #pragma unroll
-        for (int ks = 0; ks < D / 32; ++ks) {
-          const uint32_t off = (ks / 4) * 1024 + (ks % 4) * 2;      // descriptor units of 16 bytes
-          mma_f8_ss(tmem + C::kColS, q_lo + off, k_lo + off, kIdescS, ks > 0);
-        }
-        tc_commit(bar_s);
-        if (!(ok = wait_or_abort(bar_p, it & 1, abort_flag))) break;
-        if (!(ok = wait_or_abort(full_v + st, ph, abort_flag))) break;
-        tc_fence_after();
-        // O += P V: A = P codes in TMEM (8 columns per 32-key step), B = V tile MN-major (32 key rows per step)
-#pragma unroll
-        for (int ks = 0; ks < 4; ++ks) {
-#pragma unroll
-          for (int s = 0; s < C::kSub; ++s) {
-            mma_mxf8_ts(tmem + C::kColO + s * 128, tmem + C::kColS + ks * 8, v_lo + s * 1024 + ks * 256,
-                        idesc_mxf8(128, 128, false, true, ks, ks), tmem + C::kColSfa, tmem + C::kColSfb,
-                        (it > 0) || (ks > 0));
+          for (int ks = 0; ks < D / 32; ++ks) {
+            const uint32_t off = (ks / 4) * 1024 + (ks % 4) * 2;      // descriptor units of 16 bytes
+            mma_f8_ss(tmem + C::kColS, q_lo + off, k_lo + off, kIdescS, ks > 0);
           }
+          tc_commit(bar_s);
+          if (it == n_it - 1) tc_commit(bar_qfree);
+          if (!(ok = wait_or_abort(bar_p, gt & 1, abort_flag))) break;
+          if (!(ok = wait_or_abort(full_v + st, ph, abort_flag))) break;
+          tc_fence_after();
+          // O += P V: A = P codes in TMEM (8 columns per 32-key step), B = V tile MN-major (32 key rows per step).  The
+          // first chain of an item overwrites O: the softmax warps signal bar_p of that tile only after they have read
+          // the previous item's O.
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks) {
+#pragma unroll
+            for (int s = 0; s < C::kSub; ++s) {
+              mma_mxf8_ts(tmem + C::kColO + s * 128, tmem + C::kColS + ks * 8, v_lo + s * 1024 + ks * 256,
+                          idesc_mxf8(128, 128, false, true, ks, ks), tmem + C::kColSfa, tmem + C::kColSfb,
+                          (it > 0) || (ks > 0));
+            }
+          }
+          tc_commit(empty + st);
+          tc_commit(bar_o);
+          // The next S chain overwrites the P codes and scale words this chain reads.  It is issued without waiting for
+          // this one: MMAs of one CTA execute in issue order, so its first write comes after this chain's last read.
         }
-        tc_commit(empty + st);
-        tc_commit(bar_o);
-        // the next S overwrites the P codes and scale words this chain still reads: wait for it
-        if (!(ok = wait_or_abort(bar_o, it & 1, abort_flag))) break;
       }
       if (!ok) raise_abort(abort_flag, p.status, kStatusTimeoutMma);
     }
   } else {
     // ------------------------------------------------------------------------------------------ softmax / epilogue
     const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
-    const int row = qt * 128 + tid;                                       // query index inside the head
     const int nblk = p.N / 32;
-    const float qsl = p.qs[static_cast<size_t>(bh) * nblk + row / 32] * kLog2e;
-    float m = 0.f, l = 0.f;
     bool ok = true;
-    const float* ks_base = p.ks + static_cast<size_t>(bhk) * nblk;
-    const float* vs_base = p.vs + static_cast<size_t>(bhk) * nblk;
-    float4 ks4 = *reinterpret_cast<const float4*>(ks_base + kt_first * 4);
-    float4 vs4 = *reinterpret_cast<const float4*>(vs_base + kt_first * 4);
-    // One key tile.  kDiag: the tile on the diagonal of a causal problem (always the first one visited), where keys
-    // above the query index are masked; it is a compile-time variant so that the other tiles carry no select per element.
-    auto tile = [&](int it, auto diag_tag) -> bool {
-      constexpr bool kDiag = decltype(diag_tag)::value;
-      const int kt = kt_first - it;
-      const float cb[4] = {qsl * ks4.x, qsl * ks4.y, qsl * ks4.z, qsl * ks4.w};
-      const uint32_t sfb = pack4(scale_to_sb(vs4.x), scale_to_sb(vs4.y), scale_to_sb(vs4.z), scale_to_sb(vs4.w));
-      if (it + 1 < n_it) {                     // scales of the next key tile: in flight while this tile is processed
-        ks4 = *reinterpret_cast<const float4*>(ks_base + (kt - 1) * 4);
-        vs4 = *reinterpret_cast<const float4*>(vs_base + (kt - 1) * 4);
-      }
-      if (!wait_warp(bar_s, it & 1, abort_flag)) return false;
-      tc_fence_after();
-      float bsum[4], kb[4], bmax[4];
-      uint32_t r[2][32];
-      tmem_ld32(tmem + lane_base + C::kColS, r[0]);
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t (&rc)[32] = r[c & 1];
-        tmem_wait_ld();
-        if (c < 3) tmem_ld32(tmem + lane_base + C::kColS + 32 * (c + 1), r[(c + 1) & 1]);   // next chunk in flight
-        if (kDiag) {
-#pragma unroll
-          for (int e = 0; e < 32; ++e)
-            if (32 * c + e > tid) rc[e] = 0xff800000u;       // -inf: key index above the query index
-        }
-        float2 s2[16];
-#pragma unroll
-        for (int e = 0; e < 16; ++e) s2[e] = make_float2(__uint_as_float(rc[2 * e]), __uint_as_float(rc[2 * e + 1]));
-        bmax[c] = max32(s2) * cb[c];
-        kb[c] = fmaxf(floorf(bmax[c]), -1e30f);
-        const float2 c2 = splat2(cb[c]), bias2 = splat2(7.0f - kb[c]);
-        float2 sum0 = make_float2(0.f, 0.f), sum1 = make_float2(0.f, 0.f);
-        uint32_t codes[8];
-#pragma unroll
-        for (int e = 0; e < 16; e += 2) {
-          const float2 p0 = ex2_2(fma2(s2[e], c2, bias2));
-          const float2 p1 = ex2_2(fma2(s2[e + 1], c2, bias2));
-          sum0 = add2(sum0, p0);
-          sum1 = add2(sum1, p1);
-          codes[e / 2] = cvt_e4m3x4(p0.x, p0.y, p1.x, p1.y);
-        }
-        sum0 = add2(sum0, sum1);
-        bsum[c] = sum0.x + sum0.y;
-        tmem_st8(tmem + lane_base + C::kColS + 8 * c, codes);
-      }
-      const float mcand = ceilf(fmaxf(fmaxf(bmax[0], bmax[1]), fmaxf(bmax[2], bmax[3])));
-      float acc_scale = 1.0f;
-      if (it == 0) {
-        m = mcand;
-      } else if (mcand > m + 32.0f) {
-        acc_scale = sb_to_scale(static_cast<uint32_t>(max(0, min(__float2int_rn(m - mcand) + 127, 254))));
-        m = mcand;
-      }
-      if (it > 0 && __any_sync(0xffffffffu, acc_scale != 1.0f)) {
-        // rare: the running max moved by more than 32 binades; rescale this warp's O rows in place
-        for (int c = 0; c < D / 32; ++c) {
-          uint32_t r[32];
-          tmem_ld32(tmem + lane_base + C::kColO + 32 * c, r);
-          tmem_wait_ld();
-#pragma unroll
-          for (int e = 0; e < 32; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) * acc_scale);
-          tmem_st32(tmem + lane_base + C::kColO + 32 * c, r);
-        }
-      }
-      l *= acc_scale;
-      uint32_t sb[4];
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        const int e = __float2int_rn(kb[c] - 7.0f - m);      // saturates for fully masked blocks
-        sb[c] = static_cast<uint32_t>(max(0, min(max(e, -1000) + 127, 254)));
-        l = fmaf(bsum[c], __uint_as_float(sb[c] << 23), l);
-      }
-      const uint32_t sfa = pack4(sb[0], sb[1], sb[2], sb[3]);
-      tmem_st4(tmem + lane_base + C::kColSfa, sfa, sfa, sfa, sfa);
-      tmem_st4(tmem + lane_base + C::kColSfb, sfb, sfb, sfb, sfb);
-      tmem_wait_st();
-      tc_fence_before();
-      mbar_arrive(bar_p);
-      return true;
+    int gt = 0;
+#ifdef DM_PROFILE
+    long long prof[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    long long prof_tiles = 0, prof_items = 0;
+#endif
+    // scalars of an item: head, query row, first key tile; the scales of item + 1 are requested one item ahead
+    auto item_qs = [&](int item) -> const float* {
+      const int qt = n_qt - 1 - item / BH, bh = item % BH;
+      return p.qs + static_cast<size_t>(bh) * nblk + (qt * 128 + tid) / 32;
     };
-    ok = p.causal ? tile(0, std::true_type{}) : tile(0, std::false_type{});
-    for (int it = 1; ok && it < n_it; ++it) ok = tile(it, std::false_type{});
-    if (ok) ok = wait_warp(bar_o, (n_it - 1) & 1, abort_flag);
-    if (!ok) {
-      raise_abort(abort_flag, p.status, kStatusTimeoutCompute);
-    } else {
+    auto item_kv = [&](int item, const float* base) -> const float* {
+      const int qt = n_qt - 1 - item / BH, bh = item % BH;
+      const int bhk = (bh / p.H) * p.Hk + (bh % p.H) / rep;
+      return base + static_cast<size_t>(bhk) * nblk + (p.causal ? qt : (n_qt - 1)) * 4;
+    };
+    float qs_next = 0.f;
+    float4 ks4 = make_float4(0.f, 0.f, 0.f, 0.f), vs4 = ks4;
+    if (first_item < n_items) {
+      qs_next = *item_qs(first_item);
+      ks4 = *reinterpret_cast<const float4*>(item_kv(first_item, p.ks));
+      vs4 = *reinterpret_cast<const float4*>(item_kv(first_item, p.vs));
+    }
+    for (int item = first_item; item < n_items; item += item_step) {
+      DM_PROF_T(ti0);
+      const int qt = n_qt - 1 - item / BH, bh = item % BH;
+      const int b = bh / p.H, h = bh % p.H;
+      const int n_it = p.causal ? (qt + 1) : n_qt;
+      const int row = qt * 128 + tid;                                       // query index inside the head
+      const float qsl = qs_next * kLog2e;
+      const int item_n = item + item_step;
+      const bool has_next = item_n < n_items;
+      if (has_next) qs_next = *item_qs(item_n);
+      const float* ks_ptr = item_kv(item, p.ks);                            // scales of the tile being processed
+      const float* vs_ptr = item_kv(item, p.vs);
+      float m = 0.f, l = 0.f;
+      // One key tile.  kDiag: the tile on the diagonal of a causal problem (always the first one visited), where keys
+      // above the query index are masked; a compile-time variant so that the other tiles carry no select per element.
+      auto tile = [&](int it, auto diag_tag) -> bool {
+        constexpr bool kDiag = decltype(diag_tag)::value;
+        DM_PROF_T(t0);
+        const float cb[4] = {qsl * ks4.x, qsl * ks4.y, qsl * ks4.z, qsl * ks4.w};
+        const uint32_t sfb = pack4(scale_to_sb(vs4.x), scale_to_sb(vs4.y), scale_to_sb(vs4.z), scale_to_sb(vs4.w));
+        // scales of the next key tile (of this item or of the next one): in flight while this tile is processed
+        if (it + 1 < n_it) {
+          ks_ptr -= 4;
+          vs_ptr -= 4;
+          ks4 = *reinterpret_cast<const float4*>(ks_ptr);
+          vs4 = *reinterpret_cast<const float4*>(vs_ptr);
+        } else if (has_next) {
+          ks4 = *reinterpret_cast<const float4*>(item_kv(item_n, p.ks));
+          vs4 = *reinterpret_cast<const float4*>(item_kv(item_n, p.vs));
+        }
+        if (!wait_warp(bar_s, gt & 1, abort_flag)) return false;
+        DM_PROF_T(t1);
+        DM_PROF_ADD(0, t0, t1);
+        tc_fence_after();
+        float bsum[4], kb[4], bmax[4];
+        uint32_t r[2][32];
+        tmem_ld32(tmem + lane_base + C::kColS, r[0]);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t (&rc)[32] = r[c & 1];
+          tmem_wait_ld();
+          if (c < 3) tmem_ld32(tmem + lane_base + C::kColS + 32 * (c + 1), r[(c + 1) & 1]);   // next chunk in flight
+          if (kDiag) {
+#pragma unroll
+            for (int e = 0; e < 32; ++e)
+              if (32 * c + e > tid) rc[e] = 0xff800000u;       // -inf: key index above the query index
+          }
+          float2 s2[16];
+#pragma unroll
+          for (int e = 0; e < 16; ++e) s2[e] = make_float2(__uint_as_float(rc[2 * e]), __uint_as_float(rc[2 * e + 1]));
+          bmax[c] = max32(s2) * cb[c];
+          kb[c] = fmaxf(floorf(bmax[c]), -1e30f);
+          const float2 c2 = splat2(cb[c]), bias2 = splat2(7.0f - kb[c]);
+          float2 sum0 = make_float2(0.f, 0.f), sum1 = make_float2(0.f, 0.f);
+          uint32_t codes[8];
+#pragma unroll
+          for (int e = 0; e < 16; e += 2) {
+            const float2 p0 = ex2_2(fma2(s2[e], c2, bias2));
+            const float2 p1 = ex2_2(fma2(s2[e + 1], c2, bias2));
+            sum0 = add2(sum0, p0);
+            sum1 = add2(sum1, p1);
+            codes[e / 2] = cvt_e4m3x4(p0.x, p0.y, p1.x, p1.y);
+          }
+          sum0 = add2(sum0, sum1);
+          bsum[c] = sum0.x + sum0.y;
+          tmem_st8(tmem + lane_base + C::kColS + 8 * c, codes);
+        }
+        DM_PROF_T(t2);
+        DM_PROF_ADD(1, t1, t2);
+        const float mcand = ceilf(fmaxf(fmaxf(bmax[0], bmax[1]), fmaxf(bmax[2], bmax[3])));
+        float acc_scale = 1.0f;
+        if (it == 0) {
+          m = mcand;
+        } else if (mcand > m + 32.0f) {
+          acc_scale = sb_to_scale(static_cast<uint32_t>(max(0, min(__float2int_rn(m - mcand) + 127, 254))));
+          m = mcand;
+        }
+        if (it > 0 && __any_sync(0xffffffffu, acc_scale != 1.0f)) {
+          // rare: the running max moved by more than 32 binades; rescale this warp's O rows in place
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t ro[32];
+            tmem_ld32(tmem + lane_base + C::kColO + 32 * c, ro);
+            tmem_wait_ld();
+#pragma unroll
+            for (int e = 0; e < 32; ++e) ro[e] = __float_as_uint(__uint_as_float(ro[e]) * acc_scale);
+            tmem_st32(tmem + lane_base + C::kColO + 32 * c, ro);
+          }
+        }
+        l *= acc_scale;
+        uint32_t sb[4];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const int e = __float2int_rn(kb[c] - 7.0f - m);      // saturates for fully masked blocks
+          sb[c] = static_cast<uint32_t>(max(0, min(max(e, -1000) + 127, 254)));
+          l = fmaf(bsum[c], __uint_as_float(sb[c] << 23), l);
+        }
+        const uint32_t sfa = pack4(sb[0], sb[1], sb[2], sb[3]);
+        tmem_st4(tmem + lane_base + C::kColSfa, sfa, sfa, sfa, sfa);
+        tmem_st4(tmem + lane_base + C::kColSfb, sfb, sfb, sfb, sfb);
+        tmem_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if ((tid & 31) == 0) mbar_arrive(bar_p);
+        ++gt;
+        DM_PROF_T(t3);
+        DM_PROF_ADD(2, t2, t3);
+        return true;
+      };
+      ok = p.causal ? tile(0, std::true_type{}) : tile(0, std::false_type{});
+      for (int it = 1; ok && it < n_it; ++it) ok = tile(it, std::false_type{});
+      DM_PROF_T(ti1);
+      if (ok) ok = wait_warp(bar_o, (gt - 1) & 1, abort_flag);
+      if (!ok) break;
+      DM_PROF_T(ti2);
+      DM_PROF_ADD(3, ti1, ti2);
       tc_fence_after();
       const float inv_l = 1.0f / l;
       __nv_bfloat16* orow = p.o + static_cast<int64_t>(b) * p.o_sb + static_cast<int64_t>(row) * p.o_sn +
@@ -274,22 +345,27 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         for (int e = 0; e < 4; ++e) dst[e] = make_uint4(w[4 * e], w[4 * e + 1], w[4 * e + 2], w[4 * e + 3]);
       }
       p.lse[static_cast<size_t>(bh) * p.N + row] = (m + log2f(l)) * kLn2;
+      DM_PROF_T(ti3);
+      DM_PROF_ADD(4, ti2, ti3);
+      DM_PROF_ADD(5, ti0, ti3);
+#ifdef DM_PROFILE
+      prof_tiles += n_it;
+      ++prof_items;
+#endif
     }
+    if (!ok) raise_abort(abort_flag, p.status, kStatusTimeoutCompute);
+#ifdef DM_PROFILE
+    if (blockIdx.x == 0 && tid == 0) {
+      for (int i = 0; i < 8; ++i) g_fwd1_prof[i] = prof[i];
+      g_fwd1_prof[8] = prof_tiles;
+      g_fwd1_prof[9] = prof_items;
+    }
+#endif
   }
   tc_fence_before();
   __syncthreads();
   if (warp == 5) tmem_dealloc(tmem, C::kTmemCols);
 }
-
-#ifdef DM_PROFILE
-// Tuning build only (-DDM_PROFILE): cycle counters of softmax warp 0 of the first CTA, read back with cudaMemcpyFromSymbol.
-__device__ long long g_fwd_prof[16];
-#define DM_PROF_T(var) const long long var = clock64()
-#define DM_PROF_ADD(slot, a, b) prof[slot] += (b) - (a)
-#else
-#define DM_PROF_T(var)
-#define DM_PROF_ADD(slot, a, b)
-#endif
 
 // ================================================================================================ pipelined (D = 128)
 // One CTA per SM, 576 threads.  Warps 0-15: four softmax groups of four warps; group g owns key block g (32 keys) of
@@ -600,12 +676,22 @@ static cudaError_t launch_fwd_t(const CUtensorMap& tq, const CUtensorMap& tk, co
     if (e != cudaSuccess) return e;
     attr_set[dev] = true;
   }
-  dim3 grid(p.N / 128, p.B * p.H);
-  fwd_kernel<D><<<grid, 192, C::kSmemBytes, stream>>>(tq, tk, tv, p);
+  static int sm_count[64] = {};
+  if (dev >= 0 && dev < 64 && sm_count[dev] == 0) {
+    cudaError_t e = cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) return e;
+  }
+  const int sms = (dev >= 0 && dev < 64) ? sm_count[dev] : 148;
+  const int items = (p.N / 128) * p.B * p.H;
+  const int ctas = sms * ((D == 128) ? 2 : 1);              // co-resident CTAs: 256 of the 512 TMEM columns each at D = 128
+  fwd_kernel<D><<<items < ctas ? items : ctas, 192, C::kSmemBytes, stream>>>(tq, tk, tv, p);
   return cudaGetLastError();
 }
 
 #ifdef DM_PROFILE
+extern "C" int dm_prof_read_fwd1(long long* host16) {
+  return static_cast<int>(cudaMemcpyFromSymbol(host16, dm::g_fwd1_prof, sizeof(long long) * 16));
+}
 extern "C" int dm_prof_read_fwd(long long* host16) {
   return static_cast<int>(cudaMemcpyFromSymbol(host16, g_fwd_prof, sizeof(long long) * 16));
 }
