@@ -620,14 +620,11 @@ bwd_dkdv_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             tmem_st4(tmem + lane_base + C::kColXv + 4 * (blk0 + c), xv[c], xv[c], xv[c], xv[c]);
           }
           if (wg == 0) tmem_st4(tmem + lane_base + C::kColOne, 0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu);
-          tmem_wait_st();
-          tc_fence_before();
-          __syncwarp();
-          if ((tid & 31) == 0) mbar_arrive(bar_pv);
         }
         DM_PROF_T(t5);
         DM_PROF_ADD(4, t4, t5);
       }
+      // dP^T (its chain was issued when S^T was handed back) is requested while the code stores are still in flight
       DM_PROF_T(t6);
       if (ok) ok = wait_warp(bar_dp, ph, abort_flag);
       DM_PROF_T(t7);
@@ -637,6 +634,10 @@ bwd_dkdv_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         uint32_t rd[CH][32];
 #pragma unroll
         for (int c = 0; c < CH; ++c) tmem_ld32(tmem + lane_base + C::kColSd + 32 * (blk0 + c), rd[c]);
+        tmem_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if ((tid & 31) == 0) mbar_arrive(bar_pv);
         tmem_wait_ld();
         tc_fence_before();
         __syncwarp();

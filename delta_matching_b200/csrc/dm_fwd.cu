@@ -23,6 +23,7 @@ namespace dm {
 // Tuning build only (-DDM_PROFILE): cycle counters of softmax warp 0 of the first CTA, read back with cudaMemcpyFromSymbol.
 __device__ long long g_fwd_prof[16];
 __device__ long long g_fwd1_prof[16];   // serial kernel
+__device__ long long g_fwd1_cta[4 * 1024];  // per CTA: start ns, end ns, tiles, SM id
 #define DM_PROF_T(var) const long long var = clock64()
 #define DM_PROF_ADD(slot, a, b) prof[slot] += (b) - (a)
 #else
@@ -192,6 +193,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
 #ifdef DM_PROFILE
     long long prof[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     long long prof_tiles = 0, prof_items = 0;
+    const uint64_t prof_start_ns = global_ns();
 #endif
     // scalars of an item: head, query row, first key tile; the scales of item + 1 are requested one item ahead
     auto item_qs = [&](int item) -> const float* {
@@ -359,6 +361,14 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       for (int i = 0; i < 8; ++i) g_fwd1_prof[i] = prof[i];
       g_fwd1_prof[8] = prof_tiles;
       g_fwd1_prof[9] = prof_items;
+    }
+    if (tid == 0 && blockIdx.x < 1024) {
+      uint32_t smid;
+      asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+      g_fwd1_cta[4 * blockIdx.x + 0] = static_cast<long long>(prof_start_ns);
+      g_fwd1_cta[4 * blockIdx.x + 1] = static_cast<long long>(global_ns());
+      g_fwd1_cta[4 * blockIdx.x + 2] = prof_tiles;
+      g_fwd1_cta[4 * blockIdx.x + 3] = smid;
     }
 #endif
   }
@@ -689,6 +699,9 @@ static cudaError_t launch_fwd_t(const CUtensorMap& tq, const CUtensorMap& tk, co
 }
 
 #ifdef DM_PROFILE
+extern "C" int dm_prof_read_fwd1_cta(long long* host4096) {
+  return static_cast<int>(cudaMemcpyFromSymbol(host4096, dm::g_fwd1_cta, sizeof(long long) * 4096));
+}
 extern "C" int dm_prof_read_fwd1(long long* host16) {
   return static_cast<int>(cudaMemcpyFromSymbol(host16, dm::g_fwd1_prof, sizeof(long long) * 16));
 }
