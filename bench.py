@@ -23,6 +23,7 @@ import statistics
 import subprocess
 import sys
 import tempfile
+import threading
 import time
 
 import torch
@@ -52,54 +53,60 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """nvidia-smi clock / throttle-reason samples of one GPU taken every 200 ms while the timed region runs."""
-    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    """SM clock, power and clock-event reasons of one GPU, read through NVML from a thread every few milliseconds while
+    the timed region runs (read-only queries; nothing on the GPU is set).  CUDA_VISIBLE_DEVICES is honoured."""
+    REASONS = (("hw_slowdown", 0x8), ("hw_thermal_slowdown", 0x40), ("sw_thermal_slowdown", 0x20), ("sw_power_cap", 0x4))
 
-    def __init__(self, index):
-        self.index, self.proc, self.path = index, None, None
+    def __init__(self, index, period_s=0.005):
+        self.index, self.period = index, period_s
+        self.samples, self.thread, self.stop, self.max_mhz = [], None, False, None
+
+    def _physical_index(self):
+        vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+        if vis:
+            ids = [x.strip() for x in vis.split(",") if x.strip()]
+            if self.index < len(ids) and ids[self.index].isdigit():
+                return int(ids[self.index])
+        return self.index
+
+    def _run(self, nv, handle):
+        while not self.stop:
+            try:
+                self.samples.append((nv.nvmlDeviceGetClockInfo(handle, nv.NVML_CLOCK_SM),
+                                     nv.nvmlDeviceGetPowerUsage(handle) / 1000.0,
+                                     nv.nvmlDeviceGetCurrentClocksEventReasons(handle)))
+            except Exception:
+                pass
+            time.sleep(self.period)
 
     def __enter__(self):
         try:
-            fd, self.path = tempfile.mkstemp(suffix=".csv")
-            os.close(fd)
-            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
-                                          "--format=csv,noheader,nounits", "-lms", "200"],
-                                         stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+            import pynvml as nv
+            nv.nvmlInit()
+            handle = nv.nvmlDeviceGetHandleByIndex(self._physical_index())
+            self.max_mhz = float(nv.nvmlDeviceGetMaxClockInfo(handle, nv.NVML_CLOCK_SM))
+            self.thread = threading.Thread(target=self._run, args=(nv, handle), daemon=True)
+            self.thread.start()
         except Exception:
-            self.proc = None
+            self.thread = None
         return self
 
     def __exit__(self, *a):
-        if self.proc is not None:
-            self.proc.terminate()
-            try:
-                self.proc.wait(timeout=5)
-            except Exception:
-                self.proc.kill()
+        self.stop = True
+        if self.thread is not None:
+            self.thread.join(timeout=2)
 
     def summary(self):
-        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
-        if not self.path or not os.path.isfile(self.path):
-            return out
-        sm, reasons = [], set()
-        for line in open(self.path):
-            f = [x.strip() for x in line.split(",")]
-            if len(f) < 7:
-                continue
-            try:
-                sm.append(float(f[0]))
-                out["sm_max_mhz"] = float(f[1])
-            except ValueError:
-                continue
-            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[3:7]):
-                if v.lower().startswith("active"):
-                    reasons.add(name)
-        os.unlink(self.path)
-        if sm:
+        out = {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "samples": len(self.samples)}
+        if self.samples:
+            sm = [float(s[0]) for s in self.samples]
             busy = [x for x in sm if x > 0.5 * max(sm)] or sm
             out["sm_mhz"] = statistics.median(busy)
-        out["reasons"], out["samples"] = sorted(reasons), len(sm)
+            out["power_w_median"] = statistics.median(s[1] for s in self.samples)
+            mask = 0
+            for s in self.samples:
+                mask |= int(s[2])
+            out["reasons"] = sorted(name for name, bit in self.REASONS if mask & bit)
         return out
 
 
@@ -172,7 +179,7 @@ def run_reference(args, w, rank):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
@@ -267,7 +274,9 @@ def main():
         dev_in = [torch.empty_like(x) for x in (q, k, v, do)]
         host_out = [torch.empty(x.shape, dtype=torch.bfloat16).pin_memory() for x in (q, q, k, v)]   # o, dq, dk, dv
 
-        def step_e2e():
+        from delta_matching_b200.host import attn_step_host
+
+        def step_serial():                       # copy in, compute, copy out on one stream: nothing overlaps
             for d_, h_ in zip(dev_in, host_in):
                 d_.copy_(h_, non_blocking=True)
             lv = [t.detach().requires_grad_() for t in dev_in[:3]]
@@ -276,8 +285,14 @@ def main():
             for h_, d_ in zip(host_out, (o_.detach(), lv[0].grad, lv[1].grad, lv[2].grad)):
                 h_.copy_(d_, non_blocking=True)
 
+        def step_e2e():                          # the host-memory API: batch chunks pipelined over three streams
+            attn_step_host(*host_in, causal=True, mode="matched", out=host_out)
+
         for _ in range(2):
+            step_serial()
             step_e2e()
+        barrier()
+        ms_serial = timed(step_serial, max(3, args.steps // 2), stream)
         barrier()
         ms_e = timed(step_e2e, args.steps, stream)
         barrier()
@@ -287,7 +302,9 @@ def main():
         ms_e = float(te.item())
         e2e = {"value": world * flops / (ms_e * 1e-3) / 1e12, "unit": "TFLOPS", "ms_per_step": ms_e,
                "h2d_bytes_per_step": sum(x.numel() * 2 for x in host_in),
-               "d2h_bytes_per_step": sum(x.numel() * 2 for x in host_out)}
+               "d2h_bytes_per_step": sum(x.numel() * 2 for x in host_out),
+               "api": "delta_matching_b200.host.attn_step_host (pinned host tensors in and out, batch chunks pipelined)",
+               "ms_per_step_unpipelined": ms_serial}
     ops.check_status(dev)
 
     if rank == 0:
