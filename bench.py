@@ -241,13 +241,16 @@ def main():
     o, lse = ops.fwd_fp8(q8, k8, v8, qs, ks, vs, True)
     do8, dos, _ = ops.quant_do(doh, None)
     delta = ops.delta_fp8(q8, k8, v8, do8, qs, ks, vs, dos, lse, True)
+    # the two backward kernels share the dS workspace: pass 1 (dK / dV) writes it, pass 2 (dQ) streams it
+    ws_bytes = ops.bwd_workspace_bytes(w["B"], w["N"], w["H"], w["D"])
+    ws = torch.empty(ws_bytes, device=dev, dtype=torch.uint8) if ws_bytes > 0 else None
     parts = {
         "producers_qkv": lambda: ops.quant_qkv(qh, kh, vh),
         "forward": lambda: ops.fwd_fp8(q8, k8, v8, qs, ks, vs, True),
         "producer_do": lambda: ops.quant_do(doh, None),
         "pass0_delta": lambda: ops.delta_fp8(q8, k8, v8, do8, qs, ks, vs, dos, lse, True),
-        "bwd_dkdv": lambda: ops.bwd_fp8(q8, k8, v8, do8, qs, ks, vs, dos, lse, delta, True, parts=1),
-        "bwd_dq": lambda: ops.bwd_fp8(q8, k8, v8, do8, qs, ks, vs, dos, lse, delta, True, parts=2),
+        "bwd_dkdv": lambda: ops.bwd_fp8(q8, k8, v8, do8, qs, ks, vs, dos, lse, delta, True, parts=1, workspace=ws),
+        "bwd_dq": lambda: ops.bwd_fp8(q8, k8, v8, do8, qs, ks, vs, dos, lse, delta, True, parts=2, workspace=ws),
     }
     kernel_ms = {}
     for name, fn in parts.items():
@@ -256,7 +259,8 @@ def main():
         kernel_ms[name] = timed(fn, max(3, args.steps), stream)
     ops.check_status(dev)
     unit = 2.0 * w["B"] * w["H"] * w["N"] * w["N"] * w["D"] / 2      # one N x N x D matmul over all heads, causal
-    kernel_flops = {"forward": 2 * unit, "pass0_delta": 2 * unit, "bwd_dkdv": 4 * unit, "bwd_dq": 3 * unit}
+    kernel_flops = {"forward": 2 * unit, "pass0_delta": 2 * unit, "bwd_dkdv": 4 * unit,
+                    "bwd_dq": (1 if ws is not None else 3) * unit}     # pass 2 executes one matmul per tile
     dominant = max(kernel_flops, key=lambda n: kernel_ms[n])
     peaks, peak_src = measured_peaks()
     fp8_peak = 2.0 * peaks["bf16_tflops_sustained"]

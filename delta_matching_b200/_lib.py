@@ -37,6 +37,9 @@ SIGNATURES = {
                     _P, _L, _L, _L, _P, _L, _L, _L, _P, _L, _L, _L, _P, _P, _P, _P]),
     "dm_bwd_parts": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I,
                           _P, _L, _L, _L, _P, _L, _L, _L, _P, _L, _L, _L, _P, _P, _I, _P, _P]),
+    "dm_bwd_workspace_bytes": (_L, [_I, _I, _I, _I]),
+    "dm_bwd_ws": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I,
+                       _P, _L, _L, _L, _P, _L, _L, _L, _P, _L, _L, _L, _P, _L, _I, _P, _P]),
     "dm_dbg_mma_tile": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P, _P]),
     "dm_dbg_mma_cycles": (_I, [_P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P, _P]),
     "dm_kmean_static": (_I, [_P, _L, _L, _L, _I, _I, _I, _I, _P, _P, ctypes.c_char_p, _I]),

@@ -17,7 +17,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "libdm_b200.so")
-SOURCES = ("dm_abi.cu", "dm_quant.cu", "dm_fwd.cu", "dm_delta.cu", "dm_bwd.cu", "dm_probe.cu", "dm_static_scratch.cu")
+SOURCES = ("dm_abi.cu", "dm_quant.cu", "dm_fwd.cu", "dm_delta.cu", "dm_bwd.cu", "dm_bwd_p2.cu", "dm_probe.cu", "dm_static_scratch.cu")
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC"]
 
 

@@ -234,14 +234,15 @@ int dm_delta(const void* q8, const void* k8, const void* v8, const void* do8,
   return e == cudaSuccess ? 0 : cuda_fail(e, "matched-delta launch");
 }
 
-int dm_bwd_parts(const void* q8, const void* k8, const void* v8, const void* do8,
-                 const float* qs, const float* ks, const float* vs, const float* dos,
-                 const float* lse, const float* delta,
-                 int B, int N, int H, int Hk, int D, int causal,
-                 void* dq, int64_t dq_sb, int64_t dq_sn, int64_t dq_sh,
-                 void* dk, int64_t dk_sb, int64_t dk_sn, int64_t dk_sh,
-                 void* dv, int64_t dv_sb, int64_t dv_sn, int64_t dv_sh,
-                 float* rowsum_ds, float* sum_abs_pdp, int parts, int* status, void* stream) {
+static int bwd_impl(const void* q8, const void* k8, const void* v8, const void* do8,
+                    const float* qs, const float* ks, const float* vs, const float* dos,
+                    const float* lse, const float* delta,
+                    int B, int N, int H, int Hk, int D, int causal,
+                    void* dq, int64_t dq_sb, int64_t dq_sn, int64_t dq_sh,
+                    void* dk, int64_t dk_sb, int64_t dk_sn, int64_t dk_sh,
+                    void* dv, int64_t dv_sb, int64_t dv_sn, int64_t dv_sh,
+                    float* rowsum_ds, float* sum_abs_pdp, void* workspace, int64_t workspace_bytes, int parts,
+                    int* status, void* stream) {
   if ((parts & 3) == 0 || (parts & ~3)) return fail(DM_ERR_ARG, "delta_matching: parts must be 1 (dK/dV), 2 (dQ) or 3 (got %d)", parts);
   DM_TRY(check_shape(B, N, H, Hk, D));
   DM_TRY(check_sm100());
@@ -268,15 +269,64 @@ int dm_bwd_parts(const void* q8, const void* k8, const void* v8, const void* do8
   p.rowsum_ds = rowsum_ds; p.sum_abs_pdp = sum_abs_pdp;
   p.sm_scale = static_cast<float>(1.0 / sqrt(static_cast<double>(D)));
   p.B = B; p.H = H; p.Hk = Hk; p.N = N; p.causal = causal ? 1 : 0; p.status = status;
+  CUtensorMap tds;
+  if (workspace != nullptr) {
+    const int64_t need = dm_bwd_workspace_bytes(B, N, H, D);
+    if (need == 0) return fail(DM_ERR_ARG, "delta_matching: the dS workspace path needs head_dim 128 (got %d)", D);
+    if (workspace_bytes < need)
+      return fail(DM_ERR_ARG, "delta_matching: dS workspace of %lld bytes given, %lld needed", (long long)workspace_bytes, (long long)need);
+    DM_TRY(check_device_ptr(workspace, "workspace"));
+    if (!aligned16(workspace)) return fail(DM_ERR_ARG, "delta_matching: workspace must be 16-byte aligned");
+    const uint64_t tiles = static_cast<uint64_t>(B) * H * (N / 128) * (N / 128);
+    if (tiles * 128 >= (1ull << 31))
+      return fail(DM_ERR_ARG, "delta_matching: B * H * (N / 128)^2 = %llu tiles exceed one workspace (split the heads)", (unsigned long long)tiles);
+    p.ds_codes = static_cast<uint8_t*>(workspace);
+    p.ds_words = p.ds_codes + tiles * 16384;
+    DM_TRY(make_code_map(&tds, workspace, tiles * 128, 128));
+  }
   if (parts & 1) {
     cudaError_t e = dm::launch_bwd_dkdv(D, tq, tk, tv, td, p, static_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) return cuda_fail(e, "backward dK/dV launch");
   }
   if (parts & 2) {
-    cudaError_t e = dm::launch_bwd_dq(D, tq, tk, tv, td, p, static_cast<cudaStream_t>(stream));
+    cudaError_t e = (workspace != nullptr) ? dm::launch_bwd_dq_p2(tds, tk, p, static_cast<cudaStream_t>(stream))
+                                           : dm::launch_bwd_dq(D, tq, tk, tv, td, p, static_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) return cuda_fail(e, "backward dQ launch");
   }
   return 0;
+}
+
+int64_t dm_bwd_workspace_bytes(int B, int N, int H, int D) {
+  if (D != 128 || B <= 0 || H <= 0 || N <= 0 || (N % 128) != 0) return 0;
+  const int64_t tiles = static_cast<int64_t>(B) * H * (N / 128) * (N / 128);
+  return tiles * (16384 + 4);
+}
+
+int dm_bwd_ws(const void* q8, const void* k8, const void* v8, const void* do8,
+              const float* qs, const float* ks, const float* vs, const float* dos,
+              const float* lse, const float* delta,
+              int B, int N, int H, int Hk, int D, int causal,
+              void* dq, int64_t dq_sb, int64_t dq_sn, int64_t dq_sh,
+              void* dk, int64_t dk_sb, int64_t dk_sn, int64_t dk_sh,
+              void* dv, int64_t dv_sb, int64_t dv_sn, int64_t dv_sh,
+              void* workspace, int64_t workspace_bytes, int parts, int* status, void* stream) {
+  if (workspace == nullptr) return fail(DM_ERR_ARG, "delta_matching: workspace is NULL (dm_bwd is the entry point without one)");
+  return bwd_impl(q8, k8, v8, do8, qs, ks, vs, dos, lse, delta, B, N, H, Hk, D, causal, dq, dq_sb, dq_sn, dq_sh,
+                  dk, dk_sb, dk_sn, dk_sh, dv, dv_sb, dv_sn, dv_sh, nullptr, nullptr, workspace, workspace_bytes, parts,
+                  status, stream);
+}
+
+int dm_bwd_parts(const void* q8, const void* k8, const void* v8, const void* do8,
+                 const float* qs, const float* ks, const float* vs, const float* dos,
+                 const float* lse, const float* delta,
+                 int B, int N, int H, int Hk, int D, int causal,
+                 void* dq, int64_t dq_sb, int64_t dq_sn, int64_t dq_sh,
+                 void* dk, int64_t dk_sb, int64_t dk_sn, int64_t dk_sh,
+                 void* dv, int64_t dv_sb, int64_t dv_sn, int64_t dv_sh,
+                 float* rowsum_ds, float* sum_abs_pdp, int parts, int* status, void* stream) {
+  return bwd_impl(q8, k8, v8, do8, qs, ks, vs, dos, lse, delta, B, N, H, Hk, D, causal, dq, dq_sb, dq_sn, dq_sh,
+                  dk, dk_sb, dk_sn, dk_sh, dv, dv_sb, dv_sn, dv_sh, rowsum_ds, sum_abs_pdp, nullptr, 0, parts, status,
+                  stream);
 }
 
 int dm_bwd(const void* q8, const void* k8, const void* v8, const void* do8,

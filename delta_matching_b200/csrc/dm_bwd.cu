@@ -541,9 +541,12 @@ bwd_dkdv_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       qs_n[c] = qs_ptr[c];
       dos_n[c] = dos_ptr[c];
     }
+    int hq = hk * rep;                                   // query head of the iteration
     for (int it = 0; it < n_it; ++it) {
       const uint32_t ph = it & 1;
       const bool diag = p.causal && (qi == 0);           // the first query tile of a causal sweep is the diagonal one
+      // workspace tile of this iteration (pass 2 reads it back as dS of query tile qt0 + qi, key tile kt)
+      const size_t ws_tile = (static_cast<size_t>(b * p.H + hq) * n_t + (qt0 + qi)) * n_t + kt;
       float qs_c[CH], dos_c[CH];
 #pragma unroll
       for (int c = 0; c < CH; ++c) {
@@ -675,7 +678,10 @@ bwd_dkdv_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         st = 0;
         st_ph ^= 1;
       }
-      if (++qi == n_qi) qi = 0;
+      if (++qi == n_qi) {
+        qi = 0;
+        ++hq;
+      }
       (void)st_cur;
       DM_PROF_T(t11);
       DM_PROF_ADD(8, t10, t11);
@@ -692,7 +698,13 @@ bwd_dkdv_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         tmem_st8(tmem + lane_base + C::kColDc + 8 * (blk0 + c), w);
         const uint32_t xk = sb_mul(dsb, scale_to_sb(qs_c[c]));
         tmem_st4(tmem + lane_base + C::kColXk + 4 * (blk0 + c), xk, xk, xk, xk);
+        if (p.ds_codes != nullptr) {                     // the same codes, [key][query], for pass 2
+          uint4* dst = reinterpret_cast<uint4*>(p.ds_codes + ws_tile * 16384 + r * 128 + 32 * (blk0 + c));
+          dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+          dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+        }
       }
+      if (p.ds_codes != nullptr && wg == 0 && (tid & 31) == 0) p.ds_words[ws_tile * 4 + quad] = static_cast<uint8_t>(dsb);
       tmem_wait_st();
       tc_fence_before();
       __syncwarp();

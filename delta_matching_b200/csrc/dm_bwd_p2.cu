@@ -1,0 +1,235 @@
+// Backward pass 2 (head_dim 128): dQ = dS K from the quantised dS tiles that the dK / dV kernel left in a workspace.
+//
+// Reference structure: pass 1 writes dS codes, pass 2 multiplies them with K
+// (csrc/fq8_dq_pass2_hd128.h:407-442, launched from csrc/flash_bwd_fp8v10_launch.h:158-163).  The alternative without a
+// workspace (dm_bwd.cu: bwd_dq_kernel) recomputes S, dP and the exponentials per tile; this kernel only streams
+// 16 KiB dS^T tiles and K tiles through one block-scaled MMA chain per tile, so it is bound by the L2 / HBM stream.
+//
+// Workspace: tile (head bh, query tile qt, key tile kt) at index (bh * n_t + qt) * n_t + kt holds 128 x 128 e4m3 codes
+// as [key][query] (the layout the dK chain consumes), followed after all tiles by one 32-bit word per tile whose byte j
+// is the UE8M0 scale of key block j (32 keys) of the tile.  The tile is the A operand of dQ in MN-major form
+// (M = queries contiguous); K is the B operand in MN-major form as in the other kernels.
+//
+// One persistent CTA per SM, 320 threads: warps 0-3 write the per-tile scale words into TMEM (byte j = dS scale x K
+// scale of key block j, identical for all 128 rows), warps 4-7 write dQ out (two accumulators alternate between
+// items), warp 8 TMA, warp 9 MMA.  Items = (query tile, head), most key tiles first.
+#include <cuda_bf16.h>
+#include "dm_common.cuh"
+#include "dm_kernels.h"
+#include "dm_ptx.cuh"
+
+namespace dm {
+
+struct DqP2Cfg {
+  static constexpr int kTileBytes = 128 * 128;
+  static constexpr int kStages = 5;            // dS^T tile + K tile per stage
+  static constexpr int kThreads = 320;
+  static constexpr int kTmemCols = 512;
+  static constexpr int kColDq = 0;             // 2 x 128 fp32 columns
+  static constexpr int kColSf = 256;           // 2 x 4 columns: the tile's scale word
+  static constexpr int kColOne = 264;          // 4 columns of 0x7F7F7F7F: scale 1.0 for the B operand
+  static constexpr int kSmemDs = 0;
+  static constexpr int kSmemK = kStages * kTileBytes;
+  static constexpr int kSmemBar = 2 * kStages * kTileBytes;
+  static constexpr int kSmemBytes = kSmemBar + 256 + 1024;
+};
+
+__global__ void __launch_bounds__(DqP2Cfg::kThreads, 1)
+bwd_dq_p2_kernel(const __grid_constant__ CUtensorMap tm_ds, const __grid_constant__ CUtensorMap tm_k, const BwdParams p) {
+  using C = DqP2Cfg;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sDs = smem + C::kSmemDs;
+  uint8_t* sK = smem + C::kSmemK;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kSmemBar);
+  uint64_t* full = bars + 0;          // [kStages] both tiles of the stage landed
+  uint64_t* empty = bars + 5;         // [kStages] the stage's chain has read them (MMA commit)
+  uint64_t* sf_full = bars + 10;      // [2] scale word of the tile written (one arrival per scale warp)
+  uint64_t* sf_free = bars + 12;      // [2] the chain that read the word is done (MMA commit)
+  uint64_t* dq_full = bars + 14;      // [2] last chain of the item done (MMA commit)
+  uint64_t* dq_free = bars + 16;      // [2] accumulator read out (one arrival per epilogue warp)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 18);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 19);
+
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int n_t = p.N / 128;
+  const int BH = p.B * p.H;
+  const int n_items = n_t * BH;
+  const int rep = p.H / p.Hk;
+  const int nblk = p.N / 32;
+  const int first_item = static_cast<int>(blockIdx.x), item_step = static_cast<int>(gridDim.x);
+
+  if (tid == 0) {
+    for (int s = 0; s < C::kStages; ++s) {
+      mbar_init(full + s, 1);
+      mbar_init(empty + s, 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(sf_full + s, 4);
+      mbar_init(sf_free + s, 1);
+      mbar_init(dq_full + s, 1);
+      mbar_init(dq_free + s, 4);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 9) {
+    tmem_alloc(tmem_slot, C::kTmemCols);
+    tmem_relinquish();
+    tc_fence_before();
+  }
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp == 8) {
+    // ------------------------------------------------------------------------------------------ TMA producer
+    if (elect_one()) {
+      tma_prefetch_desc(&tm_ds);
+      tma_prefetch_desc(&tm_k);
+      bool ok = true;
+      uint32_t g = 0;
+      for (int item = first_item; ok && item < n_items; item += item_step) {
+        const int qt = n_t - 1 - item / BH, bh = item % BH;
+        const int bhk = (bh / p.H) * p.Hk + (bh % p.H) / rep;
+        const int n_it = p.causal ? (qt + 1) : n_t;
+        const int tile0 = (bh * n_t + qt) * n_t;
+        for (int it = 0; it < n_it; ++it, ++g) {
+          const uint32_t st = g % C::kStages;
+          if (g >= C::kStages && !(ok = wait_or_abort(empty + st, ((g / C::kStages) - 1) & 1, abort_flag))) break;
+          mbar_expect_tx(full + st, 2 * C::kTileBytes);
+          tma_load_2d(sDs + st * C::kTileBytes, &tm_ds, full + st, 0, (tile0 + it) * 128);
+          tma_load_2d(sK + st * C::kTileBytes, &tm_k, full + st, 0, bhk * p.N + it * 128);
+        }
+      }
+      if (!ok) raise_abort(abort_flag, p.status, kStatusTimeoutProducer);
+    }
+  } else if (warp == 9) {
+    // ------------------------------------------------------------------------------------------ MMA issuer
+    if (elect_one()) {
+      const uint32_t ds_lo0 = desc_lo(smem_u32(sDs)), k_lo0 = desc_lo(smem_u32(sK));
+      bool ok = true;
+      uint32_t g = 0, n_done = 0;
+      for (int item = first_item; ok && item < n_items; item += item_step, ++n_done) {
+        const int qt = n_t - 1 - item / BH;
+        const int n_it = p.causal ? (qt + 1) : n_t;
+        const uint32_t acc = n_done & 1;
+        // the accumulator was last used two items ago: its read-out must be complete
+        if (n_done >= 2 && !(ok = wait_or_abort(dq_free + acc, ((n_done >> 1) - 1) & 1, abort_flag))) break;
+        for (int it = 0; it < n_it; ++it, ++g) {
+          const uint32_t st = g % C::kStages, sf = g & 1;
+          if (!(ok = wait_or_abort(full + st, (g / C::kStages) & 1, abort_flag))) break;
+          if (!(ok = wait_or_abort(sf_full + sf, (g >> 1) & 1, abort_flag))) break;
+          tc_fence_after();
+          // dQ += dS K over the tile's 128 keys: A = dS^T tile read MN-major, B = K tile read MN-major; both advance
+          // by 32 key rows (4096 bytes) per step; byte ks of the scale word belongs to key block ks
+          const uint32_t ds_lo = ds_lo0 + st * (C::kTileBytes >> 4), k_lo = k_lo0 + st * (C::kTileBytes >> 4);
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks)
+            mma_mxf8_ss(tmem + C::kColDq + 128 * acc, ds_lo + ks * 256, k_lo + ks * 256,
+                        idesc_mxf8(128, 128, true, true, ks, 0), tmem + C::kColSf + 4 * sf, tmem + C::kColOne,
+                        (it > 0) || (ks > 0));
+          tc_commit(empty + st);
+          tc_commit(sf_free + sf);
+          if (it == n_it - 1) tc_commit(dq_full + acc);
+        }
+      }
+      if (!ok) raise_abort(abort_flag, p.status, kStatusTimeoutMma);
+    }
+  } else if (warp < 4) {
+    // ------------------------------------------------------------------------------------------ scale words
+    const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+    const uint32_t* words = reinterpret_cast<const uint32_t*>(p.ds_words);
+    tmem_st4(tmem + lane_base + C::kColOne, 0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu);
+    bool ok = true;
+    uint32_t g = 0;
+    for (int item = first_item; ok && item < n_items; item += item_step) {
+      const int qt = n_t - 1 - item / BH, bh = item % BH;
+      const int bhk = (bh / p.H) * p.Hk + (bh % p.H) / rep;
+      const int n_it = p.causal ? (qt + 1) : n_t;
+      const uint32_t* w_ptr = words + static_cast<size_t>(bh * n_t + qt) * n_t;
+      const float4* ks_ptr = reinterpret_cast<const float4*>(p.ks + static_cast<size_t>(bhk) * nblk);
+      uint32_t w_n = w_ptr[0];
+      float4 k_n = ks_ptr[0];
+      for (int it = 0; it < n_it; ++it, ++g) {
+        const uint32_t w = w_n;
+        const float4 k4 = k_n;
+        if (it + 1 < n_it) {
+          w_n = w_ptr[it + 1];
+          k_n = ks_ptr[it + 1];
+        }
+        const uint32_t word = pack4(sb_mul(w & 0xFF, scale_to_sb(k4.x)), sb_mul((w >> 8) & 0xFF, scale_to_sb(k4.y)),
+                                    sb_mul((w >> 16) & 0xFF, scale_to_sb(k4.z)), sb_mul(w >> 24, scale_to_sb(k4.w)));
+        const uint32_t sf = g & 1;
+        if (g >= 2 && !(ok = wait_warp(sf_free + sf, ((g >> 1) - 1) & 1, abort_flag))) break;
+        tc_fence_after();
+        tmem_st4(tmem + lane_base + C::kColSf + 4 * sf, word, word, word, word);
+        tmem_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if ((tid & 31) == 0) mbar_arrive(sf_full + sf);
+      }
+    }
+    if (!ok) raise_abort(abort_flag, p.status, kStatusTimeoutCompute);
+  } else {
+    // ------------------------------------------------------------------------------------------ dQ read-out
+    const int quad = warp & 3;
+    const int r = quad * 32 + (tid & 31);
+    const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
+    bool ok = true;
+    uint32_t n_done = 0;
+    for (int item = first_item; ok && item < n_items; item += item_step, ++n_done) {
+      const int qt = n_t - 1 - item / BH, bh = item % BH;
+      const int b = bh / p.H, h = bh % p.H;
+      const uint32_t acc = n_done & 1;
+      if (!(ok = wait_warp(dq_full + acc, (n_done >> 1) & 1, abort_flag))) break;
+      tc_fence_after();
+      __nv_bfloat16* dst = p.dq + static_cast<int64_t>(b) * p.dq_sb + static_cast<int64_t>(qt * 128 + r) * p.dq_sn +
+                           static_cast<int64_t>(h) * p.dq_sh;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t rr[32];
+        tmem_ld32(tmem + lane_base + C::kColDq + 128 * acc + 32 * c, rr);
+        tmem_wait_ld();
+        uint32_t w[16];
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+          __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(rr[2 * e]) * p.sm_scale,
+                                                   __uint_as_float(rr[2 * e + 1]) * p.sm_scale);
+          w[e] = *reinterpret_cast<uint32_t*>(&v);
+        }
+        uint4* d4 = reinterpret_cast<uint4*>(dst + 32 * c);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) d4[e] = make_uint4(w[4 * e], w[4 * e + 1], w[4 * e + 2], w[4 * e + 3]);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if ((tid & 31) == 0) mbar_arrive(dq_free + acc);
+    }
+    if (!ok) raise_abort(abort_flag, p.status, kStatusTimeoutCompute);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 9) tmem_dealloc(tmem, C::kTmemCols);
+}
+
+cudaError_t launch_bwd_dq_p2(const CUtensorMap& tds, const CUtensorMap& tk, const BwdParams& p, cudaStream_t stream) {
+  using C = DqP2Cfg;
+  static bool attr_set[64] = {};
+  static int sm_count[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(bwd_dq_p2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+    if (e != cudaSuccess) return e;
+    e = cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) return e;
+    attr_set[dev] = true;
+  }
+  const int sms = (dev >= 0 && dev < 64) ? sm_count[dev] : 148;
+  const int items = (p.N / 128) * p.B * p.H;
+  bwd_dq_p2_kernel<<<items < sms ? items : sms, C::kThreads, C::kSmemBytes, stream>>>(tds, tk, p);
+  return cudaGetLastError();
+}
+
+}  // namespace dm

@@ -205,11 +205,35 @@ def delta_fp8(q8, k8, v8, do8, qs, ks, vs, dos, lse, causal: bool):
     return delta
 
 
-def bwd_fp8(q8, k8, v8, do8, qs, ks, vs, dos, lse, delta, causal: bool, identity: bool = False, parts: int = 3):
+def bwd_workspace_bytes(B: int, N: int, H: int, D: int) -> int:
+    """Bytes of the dS workspace of the two-pass backward (0: the path does not apply, head_dim != 128)."""
+    return int(_lib.lib().dm_bwd_workspace_bytes(int(B), int(N), int(H), int(D)))
+
+
+def _workspace_cap_bytes() -> int:
+    """DM_BWD_WORKSPACE_MB bounds the dS workspace of one backward call (default 16384; 0 selects the backward that
+    recomputes instead of storing).  The reference bounds the same buffer with DM_BWD_* knobs and its head-group split
+    (delta_matching/attn.py:88-112)."""
+    try:
+        return int(os.environ.get("DM_BWD_WORKSPACE_MB", "16384")) << 20
+    except ValueError:
+        return 16384 << 20
+
+
+_MAX_WS_TILES = (1 << 24) - 1
+
+
+def bwd_fp8(q8, k8, v8, do8, qs, ks, vs, dos, lse, delta, causal: bool, identity: bool = False, parts: int = 3,
+            workspace=None):
     """-> (dq (B, N, H, D), dk (B, N, Hk, D), dv (B, N, Hk, D)) bf16; dk / dv are already reduced over the GQA group.
     identity=True also returns (rowsum_dS, sum_abs_PdP), fp32 (B, H, N), accumulated in the kernel before dS is
     quantised.  parts: 1 = only the dK / dV kernel, 2 = only the dQ kernel, 3 = both (the outputs of a kernel that did
-    not run are uninitialised).  Replaces the bwd_fp8_t op and the group fold of delta_matching/attn.py:114-117."""
+    not run are uninitialised).  Replaces the bwd_fp8_t op and the group fold of delta_matching/attn.py:114-117.
+
+    head_dim 128 without the identity probe runs the two-pass form: the dK / dV kernel leaves the dS codes in a
+    workspace and dQ streams them (bit-identical to the recomputing kernel).  The workspace is allocated here unless
+    `workspace` (uint8, at least bwd_workspace_bytes) is given; when it would exceed DM_BWD_WORKSPACE_MB the call is
+    split over (batch, kv-head group) ranges, and when a single group exceeds it the recomputing kernel runs."""
     dev = _cuda(q8, k8, v8, do8, qs, ks, vs, dos, lse, delta)
     B, H, N, D = q8.shape
     Hk = k8.shape[1]
@@ -217,18 +241,57 @@ def bwd_fp8(q8, k8, v8, do8, qs, ks, vs, dos, lse, delta, causal: bool, identity
     for name, t in (("lse", lse), ("delta", delta)):
         _require(t.dtype == torch.float32 and tuple(t.shape) == (B, H, N) and t.is_contiguous(), f"{name} must be fp32 (B, H, N)")
     L = _lib.lib()
+    rep = H // Hk
+    n_t = N // 128
+    cap = _workspace_cap_bytes()
+    group_bytes = bwd_workspace_bytes(1, N, rep, D)
+    two_pass = (D == 128 and not identity and group_bytes > 0 and (workspace is not None or group_bytes <= cap)
+                and rep * n_t * n_t <= _MAX_WS_TILES)
     with torch.cuda.device(dev):
         dq = torch.empty(B, N, H, D, device=dev, dtype=torch.bfloat16)
         dk = torch.empty(B, N, Hk, D, device=dev, dtype=torch.bfloat16)
         dv = torch.empty(B, N, Hk, D, device=dev, dtype=torch.bfloat16)
         rs = torch.empty(B, H, N, device=dev, dtype=torch.float32) if identity else None
         ap = torch.empty(B, H, N, device=dev, dtype=torch.float32) if identity else None
-        _lib.check(L.dm_bwd_parts(_ptr(q8), _ptr(k8), _ptr(v8), _ptr(do8), _ptr(qs), _ptr(ks), _ptr(vs), _ptr(dos),
-                            _ptr(lse), _ptr(delta), B, N, H, Hk, D, int(bool(causal)),
-                            _ptr(dq), dq.stride(0), dq.stride(1), dq.stride(2),
-                            _ptr(dk), dk.stride(0), dk.stride(1), dk.stride(2),
-                            _ptr(dv), dv.stride(0), dv.stride(1), dv.stride(2),
-                            _ptr(rs), _ptr(ap), int(parts), _ptr(status_word(dev)), _stream(q8)))
+        st = _ptr(status_word(dev))
+        if not two_pass:
+            _lib.check(L.dm_bwd_parts(_ptr(q8), _ptr(k8), _ptr(v8), _ptr(do8), _ptr(qs), _ptr(ks), _ptr(vs), _ptr(dos),
+                                      _ptr(lse), _ptr(delta), B, N, H, Hk, D, int(bool(causal)),
+                                      _ptr(dq), dq.stride(0), dq.stride(1), dq.stride(2),
+                                      _ptr(dk), dk.stride(0), dk.stride(1), dk.stride(2),
+                                      _ptr(dv), dv.stride(0), dv.stride(1), dv.stride(2),
+                                      _ptr(rs), _ptr(ap), int(parts), st, _stream(q8)))
+        else:
+            if workspace is not None:
+                _require(workspace.dtype == torch.uint8 and workspace.is_contiguous() and workspace.device == dev,
+                         "workspace must be a contiguous uint8 CUDA tensor on the inputs' device")
+                cap = workspace.numel()
+            # ranges of (batch, kv-head groups) whose workspace fits: whole batches if possible, else groups of one batch
+            groups_fit = max(1, min(Hk, cap // group_bytes, _MAX_WS_TILES // (rep * n_t * n_t)))
+            if groups_fit >= Hk:
+                bs = max(1, min(B, cap // (group_bytes * Hk), _MAX_WS_TILES // (H * n_t * n_t)))
+                ranges = [(b0, min(B, b0 + bs), 0, Hk) for b0 in range(0, B, bs)]
+            else:
+                ranges = [(b, b + 1, g0, min(Hk, g0 + groups_fit)) for b in range(B) for g0 in range(0, Hk, groups_fit)]
+            need = max(bwd_workspace_bytes(b1 - b0, N, (g1 - g0) * rep, D) for b0, b1, g0, g1 in ranges)
+            if workspace is None:
+                workspace = torch.empty(need, device=dev, dtype=torch.uint8)
+            _require(workspace.numel() >= need, f"workspace of {workspace.numel()} bytes given, {need} needed")
+            for b0, b1, g0, g1 in ranges:
+                hs = slice(g0 * rep, g1 * rep)
+                gsl = slice(g0, g1)
+                v_q8, v_do8, v_qs, v_dos = q8[b0:b1, hs], do8[b0:b1, hs], qs[b0:b1, hs], dos[b0:b1, hs]
+                v_k8, v_v8, v_ks, v_vs = k8[b0:b1, gsl], v8[b0:b1, gsl], ks[b0:b1, gsl], vs[b0:b1, gsl]
+                v_lse, v_delta = lse[b0:b1, hs], delta[b0:b1, hs]
+                # either whole batches (all heads) or head ranges of one batch: every view is dense
+                v_dq, v_dk, v_dv = dq[b0:b1, :, hs], dk[b0:b1, :, gsl], dv[b0:b1, :, gsl]
+                _lib.check(L.dm_bwd_ws(_ptr(v_q8), _ptr(v_k8), _ptr(v_v8), _ptr(v_do8), _ptr(v_qs), _ptr(v_ks), _ptr(v_vs),
+                                       _ptr(v_dos), _ptr(v_lse), _ptr(v_delta), b1 - b0, N, (g1 - g0) * rep, g1 - g0, D,
+                                       int(bool(causal)),
+                                       _ptr(v_dq), dq.stride(0), dq.stride(1), dq.stride(2),
+                                       _ptr(v_dk), dk.stride(0), dk.stride(1), dk.stride(2),
+                                       _ptr(v_dv), dv.stride(0), dv.stride(1), dv.stride(2),
+                                       _ptr(workspace), workspace.numel(), int(parts), st, _stream(q8)))
         _after(dev)
     return (dq, dk, dv, rs, ap) if identity else (dq, dk, dv)
 

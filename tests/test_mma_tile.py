@@ -61,6 +61,20 @@ def _scale_words(seed, uniform_rows):
     return word[:, None].expand(128, 4).contiguous(), (by.float() - 127).exp2()
 
 
+def test_block_scaled_a_mn_major():
+    """Both operands MN-major with per-step scales that are the same for every row (the dS^T tile of the second backward
+    pass): out = sum_k s[k] A_k^T B_k."""
+    a, b = _codes(13), _codes(14)
+    sfa, sa = _scale_words(15, uniform_rows=True)
+    sfb, sb = _scale_words(16, uniform_rows=True)
+    got = _run(a, b, sfa=sfa.cuda(), sfb=sfb.cuda(), a_mn=True, b_mn=True, nk=4)
+    want = torch.zeros(128, 128, dtype=torch.float64)
+    for k in range(4):
+        blk = a[32 * k:32 * k + 32, :].double().T @ b[32 * k:32 * k + 32, :].double()
+        want += sa[0, k].double() * sb[0, k].double() * blk
+    assert torch.equal(got.double(), want)
+
+
 @pytest.mark.parametrize("a_tmem", [True, False])
 def test_block_scaled(a_tmem):
     """Per-row, per-step A scales (the P / P^T / dS^T scale words) and a per-step B scale shared by all columns (the V
