@@ -285,7 +285,8 @@ static int bwd_impl(const void* q8, const void* k8, const void* v8, const void* 
     DM_TRY(make_code_map(&tds, workspace, tiles * 128, 128));
   }
   if (parts & 1) {
-    cudaError_t e = dm::launch_bwd_dkdv(D, tq, tk, tv, td, p, static_cast<cudaStream_t>(stream));
+    cudaError_t e = dm::launch_bwd_dkdv(D, tq, tk, tv, td, (workspace != nullptr) ? &tds : nullptr, p,
+                                        static_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) return cuda_fail(e, "backward dK/dV launch");
   }
   if (parts & 2) {

@@ -361,7 +361,8 @@ struct KvPipeCfg {
   static constexpr int kSmemQ = 2 * kTileBytes;                      // [kStages]
   static constexpr int kSmemDo = kSmemQ + kStages * kTileBytes;      // [kStages]
   static constexpr int kSmemVec = kSmemDo + kStages * kTileBytes;    // [kStages] x (lse[128], delta[128]) floats
-  static constexpr int kSmemXch = kSmemVec + kStages * 1024;         // 2 x [16 warps] floats
+  static constexpr int kSmemWs = kSmemVec + kStages * 1024;          // 2 staging tiles of dS^T codes for the workspace
+  static constexpr int kSmemXch = kSmemWs + 2 * kTileBytes;          // 2 x [16 warps] floats
   static constexpr int kSmemBar = kSmemXch + 2 * 16 * 4;
   static constexpr int kSmemBytes = kSmemBar + 256 + 1024;
 };
@@ -370,7 +371,7 @@ template <int G>
 __global__ void __launch_bounds__(KvPipeCfg<G>::kThreads, 1)
 bwd_dkdv_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                      const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
-                     const BwdParams p) {
+                     const __grid_constant__ CUtensorMap tm_ds, const BwdParams p) {
   using C = KvPipeCfg<G>;
   constexpr int kW = C::kGroups * 4;                 // compute warps; warp kW = TMA, kW + 1 = MMA
   constexpr int CH = C::kChunks;
@@ -382,6 +383,7 @@ bwd_dkdv_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   uint8_t* sDo = smem + C::kSmemDo;
   float* sVec = reinterpret_cast<float*>(smem + C::kSmemVec);
   float* sXch = reinterpret_cast<float*>(smem + C::kSmemXch);
+  uint8_t* sWs = smem + C::kSmemWs;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kSmemBar);
   uint64_t* bar_kv = bars + 0;
   uint64_t* bar_s = bars + 1;        // S^T landed in the shared region (MMA commit)
@@ -509,9 +511,20 @@ bwd_dkdv_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         for (int ks = 0; ks < 4; ++ks)
           mma_mxf8_ts(tmem + C::kColDk, tmem + C::kColDc + ks * 8, q_lo + ks * 256, kIdescBs, tmem + C::kColXk + 4 * ks,
                       tmem + C::kColOne, (it > 0) || (ks > 0));
+        if (p.ds_codes != nullptr) {
+          // The compute warps also left the dS^T codes of this iteration in staging tile it & 1: send it to the
+          // workspace.  Before the commit of bar_done below, at most this store still reads shared memory, so a warp
+          // that has seen bar_done of iteration it may overwrite staging tile (it + 1) & 1.
+          const int hq_it = hk * rep + it / n_qi, qt_it = qt0 + it % n_qi;
+          const int ws_tile = ((b * p.H + hq_it) * n_t + qt_it) * n_t + kt;
+          tma_store_2d(&tm_ds, sWs + (it & 1) * C::kTileBytes, 0, ws_tile * 128);
+          bulk_commit_group();
+          bulk_wait_group_read<1>();
+        }
         tc_commit(empty + st);
         tc_commit(bar_done);
       }
+      if (p.ds_codes != nullptr) bulk_wait_group<0>();
       if (!ok) raise_abort(abort_flag, p.status, kStatusTimeoutMma);
     }
   } else {
@@ -698,12 +711,16 @@ bwd_dkdv_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         tmem_st8(tmem + lane_base + C::kColDc + 8 * (blk0 + c), w);
         const uint32_t xk = sb_mul(dsb, scale_to_sb(qs_c[c]));
         tmem_st4(tmem + lane_base + C::kColXk + 4 * (blk0 + c), xk, xk, xk, xk);
-        if (p.ds_codes != nullptr) {                     // the same codes, [key][query], for pass 2
-          uint4* dst = reinterpret_cast<uint4*>(p.ds_codes + ws_tile * 16384 + r * 128 + 32 * (blk0 + c));
-          dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
-          dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+        if (p.ds_codes != nullptr) {
+          // the same codes as a [key][query] tile in 128-byte-swizzled shared memory (16-byte chunk j of row r at
+          // chunk j ^ (r % 8)); the MMA warp's thread stores the tile to the workspace for pass 2
+          uint8_t* ws_row = sWs + ph * C::kTileBytes + r * 128;
+          const int j = 2 * (blk0 + c);
+          *reinterpret_cast<uint4*>(ws_row + ((j ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+          *reinterpret_cast<uint4*>(ws_row + (((j + 1) ^ (r & 7)) << 4)) = make_uint4(w[4], w[5], w[6], w[7]);
         }
       }
+      if (p.ds_codes != nullptr) fence_async_smem();
       if (p.ds_codes != nullptr && wg == 0 && (tid & 31) == 0) p.ds_words[ws_tile * 4 + quad] = static_cast<uint8_t>(dsb);
       tmem_wait_st();
       tc_fence_before();
@@ -1346,7 +1363,9 @@ extern "C" int dm_prof_read_kv(long long* host16) {
 #endif
 
 cudaError_t launch_bwd_dkdv(int D, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
-                            const CUtensorMap& tdo, const BwdParams& p, cudaStream_t stream) {
+                            const CUtensorMap& tdo, const CUtensorMap* tds_or_null, const BwdParams& p,
+                            cudaStream_t stream) {
+  const CUtensorMap* tds = (tds_or_null != nullptr) ? tds_or_null : &tq;     // unused by the kernel without a workspace
   if (D == 128) {
     // DM_KV_GROUPS (tuning): compute groups of the pipelined kernel, 4 (32 query columns per thread; default, 1.26 ms at
     // B=4 N=4096 H=32 Hk=8 on B200) or 2 (64 columns per thread, 1.30 ms)
@@ -1359,12 +1378,12 @@ cudaError_t launch_bwd_dkdv(int D, const CUtensorMap& tq, const CUtensorMap& tk,
       static bool done[64] = {};
       cudaError_t e = set_smem(bwd_dkdv_pipe_kernel<4>, KvPipeCfg<4>::kSmemBytes, done);
       if (e != cudaSuccess) return e;
-      bwd_dkdv_pipe_kernel<4><<<grid, KvPipeCfg<4>::kThreads, KvPipeCfg<4>::kSmemBytes, stream>>>(tq, tk, tv, tdo, p);
+      bwd_dkdv_pipe_kernel<4><<<grid, KvPipeCfg<4>::kThreads, KvPipeCfg<4>::kSmemBytes, stream>>>(tq, tk, tv, tdo, *tds, p);
     } else {
       static bool done[64] = {};
       cudaError_t e = set_smem(bwd_dkdv_pipe_kernel<2>, KvPipeCfg<2>::kSmemBytes, done);
       if (e != cudaSuccess) return e;
-      bwd_dkdv_pipe_kernel<2><<<grid, KvPipeCfg<2>::kThreads, KvPipeCfg<2>::kSmemBytes, stream>>>(tq, tk, tv, tdo, p);
+      bwd_dkdv_pipe_kernel<2><<<grid, KvPipeCfg<2>::kThreads, KvPipeCfg<2>::kSmemBytes, stream>>>(tq, tk, tv, tdo, *tds, p);
     }
     return cudaGetLastError();
   }

@@ -81,7 +81,8 @@ cudaError_t launch_fwd(int D, const CUtensorMap& tq, const CUtensorMap& tk, cons
 cudaError_t launch_delta(int D, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                          const CUtensorMap& tdo, const DeltaParams& p, cudaStream_t stream);
 cudaError_t launch_bwd_dkdv(int D, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
-                            const CUtensorMap& tdo, const BwdParams& p, cudaStream_t stream);
+                            const CUtensorMap& tdo, const CUtensorMap* tds_or_null, const BwdParams& p,
+                            cudaStream_t stream);
 cudaError_t launch_bwd_dq(int D, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                           const CUtensorMap& tdo, const BwdParams& p, cudaStream_t stream);
 cudaError_t launch_bwd_dq_p2(const CUtensorMap& tds, const CUtensorMap& tk, const BwdParams& p, cudaStream_t stream);
