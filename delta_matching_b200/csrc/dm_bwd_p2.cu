@@ -26,8 +26,9 @@ struct DqP2Cfg {
   static constexpr int kThreads = 320;
   static constexpr int kTmemCols = 512;
   static constexpr int kColDq = 0;             // 2 x 128 fp32 columns
-  static constexpr int kColSf = 256;           // 2 x 4 columns: the tile's scale word
-  static constexpr int kColOne = 264;          // 4 columns of 0x7F7F7F7F: scale 1.0 for the B operand
+  static constexpr int kSf = 4;                // scale-word buffers (tiles the scale warps may run ahead of the MMAs)
+  static constexpr int kColSf = 256;           // kSf x 4 columns: the tile's scale word
+  static constexpr int kColOne = 256 + 4 * kSf;   // 4 columns of 0x7F7F7F7F: scale 1.0 for the B operand
   static constexpr int kSmemDs = 0;
   static constexpr int kSmemK = kStages * kTileBytes;
   static constexpr int kSmemBar = 2 * kStages * kTileBytes;
@@ -44,12 +45,12 @@ bwd_dq_p2_kernel(const __grid_constant__ CUtensorMap tm_ds, const __grid_constan
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kSmemBar);
   uint64_t* full = bars + 0;          // [kStages] both tiles of the stage landed
   uint64_t* empty = bars + 5;         // [kStages] the stage's chain has read them (MMA commit)
-  uint64_t* sf_full = bars + 10;      // [2] scale word of the tile written (one arrival per scale warp)
-  uint64_t* sf_free = bars + 12;      // [2] the chain that read the word is done (MMA commit)
-  uint64_t* dq_full = bars + 14;      // [2] last chain of the item done (MMA commit)
-  uint64_t* dq_free = bars + 16;      // [2] accumulator read out (one arrival per epilogue warp)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 18);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 19);
+  uint64_t* sf_full = bars + 10;      // [kSf] scale word of the tile written (one arrival per scale warp)
+  uint64_t* sf_free = bars + 14;      // [kSf] the chain that read the word is done (MMA commit)
+  uint64_t* dq_full = bars + 18;      // [2] last chain of the item done (MMA commit)
+  uint64_t* dq_free = bars + 20;      // [2] accumulator read out (one arrival per epilogue warp)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 22);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 23);
 
   const int tid = threadIdx.x, warp = tid >> 5;
   const int n_t = p.N / 128;
@@ -64,9 +65,11 @@ bwd_dq_p2_kernel(const __grid_constant__ CUtensorMap tm_ds, const __grid_constan
       mbar_init(full + s, 1);
       mbar_init(empty + s, 1);
     }
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < C::kSf; ++s) {
       mbar_init(sf_full + s, 4);
       mbar_init(sf_free + s, 1);
+    }
+    for (int s = 0; s < 2; ++s) {
       mbar_init(dq_full + s, 1);
       mbar_init(dq_free + s, 4);
     }
@@ -117,9 +120,9 @@ bwd_dq_p2_kernel(const __grid_constant__ CUtensorMap tm_ds, const __grid_constan
         // the accumulator was last used two items ago: its read-out must be complete
         if (n_done >= 2 && !(ok = wait_or_abort(dq_free + acc, ((n_done >> 1) - 1) & 1, abort_flag))) break;
         for (int it = 0; it < n_it; ++it, ++g) {
-          const uint32_t st = g % C::kStages, sf = g & 1;
+          const uint32_t st = g % C::kStages, sf = g % C::kSf;
           if (!(ok = wait_or_abort(full + st, (g / C::kStages) & 1, abort_flag))) break;
-          if (!(ok = wait_or_abort(sf_full + sf, (g >> 1) & 1, abort_flag))) break;
+          if (!(ok = wait_or_abort(sf_full + sf, (g / C::kSf) & 1, abort_flag))) break;
           tc_fence_after();
           // dQ += dS K over the tile's 128 keys: A = dS^T tile read MN-major, B = K tile read MN-major; both advance
           // by 32 key rows (4096 bytes) per step; byte ks of the scale word belongs to key block ks
@@ -142,26 +145,64 @@ bwd_dq_p2_kernel(const __grid_constant__ CUtensorMap tm_ds, const __grid_constan
     const uint32_t* words = reinterpret_cast<const uint32_t*>(p.ds_words);
     tmem_st4(tmem + lane_base + C::kColOne, 0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu);
     bool ok = true;
+    // The tile's dS scale word and its four K scales come from global memory: they are requested kAhead tiles before
+    // they are used, through a walk over the CTA's (item, key tile) sequence that runs ahead of the consuming one.
+    constexpr int kAhead = 4;
+    struct Walk {
+      int item, it, n_it;
+      const uint32_t* w_ptr;
+      const float4* ks_ptr;
+    };
+    auto walk_set = [&](Walk& wk) {
+      if (wk.item >= n_items) return;
+      const int qt = n_t - 1 - wk.item / BH, bh = wk.item % BH;
+      const int bhk = (bh / p.H) * p.Hk + (bh % p.H) / rep;
+      wk.it = 0;
+      wk.n_it = p.causal ? (qt + 1) : n_t;
+      wk.w_ptr = words + static_cast<size_t>(bh * n_t + qt) * n_t;
+      wk.ks_ptr = reinterpret_cast<const float4*>(p.ks + static_cast<size_t>(bhk) * nblk);
+    };
+    auto walk_next = [&](Walk& wk) {
+      if (++wk.it == wk.n_it) {
+        wk.item += item_step;
+        walk_set(wk);
+      }
+    };
+    Walk pre{first_item, 0, 0, nullptr, nullptr};
+    walk_set(pre);
+    uint32_t w_q[kAhead];
+    float4 k_q[kAhead];
+#pragma unroll
+    for (int i = 0; i < kAhead; ++i) {
+      w_q[i] = 0;
+      k_q[i] = make_float4(1.f, 1.f, 1.f, 1.f);
+      if (pre.item < n_items) {
+        w_q[i] = pre.w_ptr[pre.it];
+        k_q[i] = pre.ks_ptr[pre.it];
+        walk_next(pre);
+      }
+    }
     uint32_t g = 0;
     for (int item = first_item; ok && item < n_items; item += item_step) {
-      const int qt = n_t - 1 - item / BH, bh = item % BH;
-      const int bhk = (bh / p.H) * p.Hk + (bh % p.H) / rep;
+      const int qt = n_t - 1 - item / BH;
       const int n_it = p.causal ? (qt + 1) : n_t;
-      const uint32_t* w_ptr = words + static_cast<size_t>(bh * n_t + qt) * n_t;
-      const float4* ks_ptr = reinterpret_cast<const float4*>(p.ks + static_cast<size_t>(bhk) * nblk);
-      uint32_t w_n = w_ptr[0];
-      float4 k_n = ks_ptr[0];
       for (int it = 0; it < n_it; ++it, ++g) {
-        const uint32_t w = w_n;
-        const float4 k4 = k_n;
-        if (it + 1 < n_it) {
-          w_n = w_ptr[it + 1];
-          k_n = ks_ptr[it + 1];
+        const uint32_t w = w_q[0];
+        const float4 k4 = k_q[0];
+#pragma unroll
+        for (int i = 0; i + 1 < kAhead; ++i) {
+          w_q[i] = w_q[i + 1];
+          k_q[i] = k_q[i + 1];
+        }
+        if (pre.item < n_items) {
+          w_q[kAhead - 1] = pre.w_ptr[pre.it];
+          k_q[kAhead - 1] = pre.ks_ptr[pre.it];
+          walk_next(pre);
         }
         const uint32_t word = pack4(sb_mul(w & 0xFF, scale_to_sb(k4.x)), sb_mul((w >> 8) & 0xFF, scale_to_sb(k4.y)),
                                     sb_mul((w >> 16) & 0xFF, scale_to_sb(k4.z)), sb_mul(w >> 24, scale_to_sb(k4.w)));
-        const uint32_t sf = g & 1;
-        if (g >= 2 && !(ok = wait_warp(sf_free + sf, ((g >> 1) - 1) & 1, abort_flag))) break;
+        const uint32_t sf = g % C::kSf;
+        if (g >= C::kSf && !(ok = wait_warp(sf_free + sf, ((g / C::kSf) - 1) & 1, abort_flag))) break;
         tc_fence_after();
         tmem_st4(tmem + lane_base + C::kColSf + 4 * sf, word, word, word, word);
         tmem_wait_st();
