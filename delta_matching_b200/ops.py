@@ -211,13 +211,17 @@ def bwd_workspace_bytes(B: int, N: int, H: int, D: int) -> int:
 
 
 def _workspace_cap_bytes() -> int:
-    """DM_BWD_WORKSPACE_MB bounds the dS workspace of one backward call (default 16384; 0 selects the backward that
-    recomputes instead of storing).  The reference bounds the same buffer with DM_BWD_* knobs and its head-group split
-    (delta_matching/attn.py:88-112)."""
+    """Bound of the dS workspace of one backward call: DM_BWD_WORKSPACE_MB (MiB; 0 selects the backward that recomputes
+    instead of storing), else the reference's own knob DM_BWD_WS_LIMIT_GB (delta_matching/split.py:37-97 bounds the same
+    buffer by splitting the call per head group), else 16 GiB."""
     try:
-        return int(os.environ.get("DM_BWD_WORKSPACE_MB", "16384")) << 20
+        if "DM_BWD_WORKSPACE_MB" in os.environ:
+            return int(os.environ["DM_BWD_WORKSPACE_MB"]) << 20
+        if "DM_BWD_WS_LIMIT_GB" in os.environ:
+            return int(float(os.environ["DM_BWD_WS_LIMIT_GB"]) * (1 << 30))
     except ValueError:
-        return 16384 << 20
+        pass
+    return 16384 << 20
 
 
 _MAX_WS_TILES = (1 << 24) - 1

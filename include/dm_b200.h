@@ -116,7 +116,8 @@ int dm_bwd_parts(const void* q8, const void* k8, const void* v8, const void* do8
 /* The backward in the reference's two-pass form, for head_dim 128: the dK / dV kernel (pass 1) also leaves the quantised
  * dS tiles in `workspace`, and dQ = dS K is a streaming kernel over them (pass 2) instead of a kernel that recomputes S,
  * dP and the exponentials (csrc/flash_bwd_fp8v10_launch.h:158-163, csrc/fq8_dq_pass2_hd128.h:407-442; the reference
- * allocates the dS buffer inside the op and bounds it with its head-group split, delta_matching/attn.py:88-112).
+ * allocates the dS buffer inside the op and bounds it with its head-group split, delta_matching/attn.py:88-112,
+ * delta_matching/split.py:37-97).
  * Outputs are bit-identical to dm_bwd.  workspace: device buffer of at least dm_bwd_workspace_bytes(B, N, H, D) bytes,
  * 16-byte aligned; contents on entry are ignored.  parts as in dm_bwd_parts; parts = 2 alone reads what an earlier
  * parts = 1 call with the same arguments wrote.  Limit: B * H * (N / 128)^2 < 2^24 tiles per call (split the heads
