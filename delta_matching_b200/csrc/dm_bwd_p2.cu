@@ -92,7 +92,7 @@ bwd_dq_p2_kernel(const __grid_constant__ CUtensorMap tm_ds, const __grid_constan
       tma_prefetch_desc(&tm_k);
       bool ok = true;
       uint32_t g = 0;
-      for (int item = first_item; ok && item < n_items; item += item_step) {
+      for (int k = 0, item; ok && (item = sched_item(k, first_item, item_step)) < n_items; ++k) {
         const int qt = n_t - 1 - item / BH, bh = item % BH;
         const int bhk = (bh / p.H) * p.Hk + (bh % p.H) / rep;
         const int n_it = p.causal ? (qt + 1) : n_t;
@@ -113,7 +113,7 @@ bwd_dq_p2_kernel(const __grid_constant__ CUtensorMap tm_ds, const __grid_constan
       const uint32_t ds_lo0 = desc_lo(smem_u32(sDs)), k_lo0 = desc_lo(smem_u32(sK));
       bool ok = true;
       uint32_t g = 0, n_done = 0;
-      for (int item = first_item; ok && item < n_items; item += item_step, ++n_done) {
+      for (int k = 0, item; ok && (item = sched_item(k, first_item, item_step)) < n_items; ++k, ++n_done) {
         const int qt = n_t - 1 - item / BH;
         const int n_it = p.causal ? (qt + 1) : n_t;
         const uint32_t acc = n_done & 1;
@@ -149,7 +149,7 @@ bwd_dq_p2_kernel(const __grid_constant__ CUtensorMap tm_ds, const __grid_constan
     // they are used, through a walk over the CTA's (item, key tile) sequence that runs ahead of the consuming one.
     constexpr int kAhead = 4;
     struct Walk {
-      int item, it, n_it;
+      int k, item, it, n_it;
       const uint32_t* w_ptr;
       const float4* ks_ptr;
     };
@@ -164,11 +164,11 @@ bwd_dq_p2_kernel(const __grid_constant__ CUtensorMap tm_ds, const __grid_constan
     };
     auto walk_next = [&](Walk& wk) {
       if (++wk.it == wk.n_it) {
-        wk.item += item_step;
+        wk.item = sched_item(++wk.k, first_item, item_step);
         walk_set(wk);
       }
     };
-    Walk pre{first_item, 0, 0, nullptr, nullptr};
+    Walk pre{0, first_item, 0, 0, nullptr, nullptr};
     walk_set(pre);
     uint32_t w_q[kAhead];
     float4 k_q[kAhead];
@@ -183,7 +183,7 @@ bwd_dq_p2_kernel(const __grid_constant__ CUtensorMap tm_ds, const __grid_constan
       }
     }
     uint32_t g = 0;
-    for (int item = first_item; ok && item < n_items; item += item_step) {
+    for (int k = 0, item; ok && (item = sched_item(k, first_item, item_step)) < n_items; ++k) {
       const int qt = n_t - 1 - item / BH;
       const int n_it = p.causal ? (qt + 1) : n_t;
       for (int it = 0; it < n_it; ++it, ++g) {
@@ -219,7 +219,7 @@ bwd_dq_p2_kernel(const __grid_constant__ CUtensorMap tm_ds, const __grid_constan
     const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
     bool ok = true;
     uint32_t n_done = 0;
-    for (int item = first_item; ok && item < n_items; item += item_step, ++n_done) {
+    for (int k = 0, item; ok && (item = sched_item(k, first_item, item_step)) < n_items; ++k, ++n_done) {
       const int qt = n_t - 1 - item / BH, bh = item % BH;
       const int b = bh / p.H, h = bh % p.H;
       const uint32_t acc = n_done & 1;

@@ -49,6 +49,15 @@ __device__ __forceinline__ void two_sum_acc(float& hi, float& lo, float x) {
   lo = __fadd_rn(lo, err);
 }
 
+// ---------------------------------------------------------------------------------------------- persistent schedule
+// Work items are numbered heaviest first.  Round k hands items k * n_ctas ... k * n_ctas + n_ctas - 1 to the CTAs in
+// ascending CTA order when k is even and in descending order when k is odd, so that the totals of the CTAs stay close to
+// each other (a CTA that got the heaviest item of one round gets the lightest of the next).  A CTA whose item of round k
+// does not exist has no item in any later round either.
+__device__ __forceinline__ int sched_item(int k, int cta, int n_ctas) {
+  return k * n_ctas + ((k & 1) ? (n_ctas - 1 - cta) : cta);
+}
+
 // ---------------------------------------------------------------------------------------------- bounded waits
 __device__ __forceinline__ uint64_t global_ns() {
   uint64_t t;

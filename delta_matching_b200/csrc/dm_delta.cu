@@ -106,7 +106,7 @@ delta_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ C
       tma_prefetch_desc(&tm_do);
       uint32_t g = 0, n_done = 0;                      // key tiles issued so far; items started so far
       bool ok = true;
-      for (int item = blockIdx.x; ok && item < n_items; item += gridDim.x, ++n_done) {
+      for (int k = 0, item; ok && (item = sched_item(k, blockIdx.x, gridDim.x)) < n_items; ++k, ++n_done) {
         int qt, bh;
         delta_item(item, n_qt, bh_count, qt, bh);
         const int bhk = (bh / p.H) * p.Hk + (bh % p.H) / (p.H / p.Hk);
@@ -138,7 +138,7 @@ delta_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ C
       const uint32_t k_lo0 = desc_lo(smem_u32(sK)), v_lo0 = desc_lo(smem_u32(sV));
       uint32_t g = 0, n_done = 0;
       bool ok = true;
-      for (int item = blockIdx.x; ok && item < n_items; item += gridDim.x, ++n_done) {
+      for (int k = 0, item; ok && (item = sched_item(k, blockIdx.x, gridDim.x)) < n_items; ++k, ++n_done) {
         int qt, bh;
         delta_item(item, n_qt, bh_count, qt, bh);
         const int n_it = p.causal ? (qt + 1) : n_qt;
@@ -176,7 +176,7 @@ delta_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ C
     const int nblk = p.N / 32;
     uint32_t g = 0, n_done = 0;
     bool ok = true;
-    for (int item = blockIdx.x; item < n_items; item += gridDim.x, ++n_done) {
+    for (int k = 0, item; (item = sched_item(k, blockIdx.x, gridDim.x)) < n_items; ++k, ++n_done) {
       int qt, bh;
       delta_item(item, n_qt, bh_count, qt, bh);
       const int bhk = (bh / p.H) * p.Hk + (bh % p.H) / (p.H / p.Hk);

@@ -49,8 +49,8 @@ struct FwdCfg {
   static constexpr int kSmemBytes = kSmemBar + 256 + 1024;   // + slack for the 1024-byte alignment of the tile base
 };
 
-// Persistent: the grid is (CTAs per SM) x (SMs); CTA j processes work items j, j + grid, ... of a list ordered by
-// decreasing number of key tiles (item -> query tile n_qt - 1 - item / (B H), head item % (B H)).  The three roles keep
+// Persistent: the grid is (CTAs per SM) x (SMs); CTA j processes the work items sched_item(0, j), sched_item(1, j), ...
+// of a list ordered by decreasing number of key tiles (item -> query tile n_qt - 1 - item / (B H), head item % (B H)).  The three roles keep
 // running tile / item counters for the barrier phases, so the K / V ring, the next Q tile and the next S run ahead into
 // the following item while the softmax warps still write out O of the current one.
 template <int D>
@@ -114,7 +114,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       tma_prefetch_desc(&tm_v);
       bool ok = true;
       int gt = 0, ic = 0;                                 // tiles and items issued so far by this CTA
-      for (int item = first_item; ok && item < n_items; item += item_step, ++ic) {
+      for (int k = 0, item; ok && (item = sched_item(k, first_item, item_step)) < n_items; ++k, ++ic) {
         const int qt = n_qt - 1 - item / BH, bh = item % BH;
         const int bhk = (bh / p.H) * p.Hk + (bh % p.H) / rep;
         const int n_it = p.causal ? (qt + 1) : n_qt;
@@ -143,7 +143,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       const uint32_t q_lo = desc_lo(smem_u32(sQ)), k_lo0 = desc_lo(smem_u32(sK)), v_lo0 = desc_lo(smem_u32(sV));
       bool ok = true;
       int gt = 0, ic = 0;
-      for (int item = first_item; ok && item < n_items; item += item_step, ++ic) {
+      for (int k = 0, item; ok && (item = sched_item(k, first_item, item_step)) < n_items; ++k, ++ic) {
         const int qt = n_qt - 1 - item / BH;
         const int n_it = p.causal ? (qt + 1) : n_qt;
         if (!(ok = wait_or_abort(bar_q, ic & 1, abort_flag))) break;
@@ -212,14 +212,14 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       ks4 = *reinterpret_cast<const float4*>(item_kv(first_item, p.ks));
       vs4 = *reinterpret_cast<const float4*>(item_kv(first_item, p.vs));
     }
-    for (int item = first_item; item < n_items; item += item_step) {
+    for (int k = 0, item; (item = sched_item(k, first_item, item_step)) < n_items; ++k) {
       DM_PROF_T(ti0);
       const int qt = n_qt - 1 - item / BH, bh = item % BH;
       const int b = bh / p.H, h = bh % p.H;
       const int n_it = p.causal ? (qt + 1) : n_qt;
       const int row = qt * 128 + tid;                                       // query index inside the head
       const float qsl = qs_next * kLog2e;
-      const int item_n = item + item_step;
+      const int item_n = sched_item(k + 1, first_item, item_step);
       const bool has_next = item_n < n_items;
       if (has_next) qs_next = *item_qs(item_n);
       const float* ks_ptr = item_kv(item, p.ks);                            // scales of the tile being processed
