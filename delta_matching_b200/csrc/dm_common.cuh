@@ -69,6 +69,7 @@ __device__ __forceinline__ uint64_t global_ns() {
 // raised the abort flag.  Returns false on give-up; the caller records a status code, raises the flag and leaves its loop.
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
 __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_test_wait(bar, parity)) return true;      // the common case in a pipeline that runs ahead: already complete
   if (mbar_try_wait(bar, parity)) return true;
   // A waiting warp must not eat the issue slots of the warps it waits for: after a few immediate retries it sleeps
   // between polls, and it looks at the abort flag and the clock only every 256 polls.
@@ -90,6 +91,7 @@ __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, vo
 // Whole-warp form for the compute warps: every lane polls, the verdict is made uniform so that the warp-wide tcgen05.ld /
 // tcgen05.st that follow are never executed by a part of the warp.
 __device__ __forceinline__ bool wait_warp(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  if (__all_sync(0xffffffffu, mbar_test_wait(bar, parity) ? 1 : 0) != 0) return true;   // ~30 cycles when complete
   return __all_sync(0xffffffffu, wait_or_abort(bar, parity, abort_flag) ? 1 : 0) != 0;
 }
 __device__ __forceinline__ void raise_abort(volatile int* abort_flag, int* status, int code) {
