@@ -96,6 +96,9 @@ class _DMAttn(torch.autograd.Function):
         return dq.permute(0, 2, 1, 3), dk.permute(0, 2, 1, 3), dv.permute(0, 2, 1, 3), None, None
 
 
+# The kernels are reached through ctypes, which a tracing compiler cannot look into: under torch.compile this call is a
+# graph break that runs eagerly (the reference reaches the same state with opaque torch.ops, tests/test_api.py:304-317).
+@torch.compiler.disable
 def dm_attn_func_bhnd(q, k, v, causal=True, softmax_scale=None, delta_mode="stale"):
     """Attention on (B, H, N, D) inputs: q (B, H, N, D), k / v (B, Hk, N, D) bf16 on CUDA (any strides; H % Hk == 0) ->
     O (B, N, H, D) bf16 contiguous.  delta_mode: "stale" (delta = rowsum(dO * O)) or "matched" (the Delta-Matching
