@@ -9,8 +9,8 @@
 //   SFA_b = UE8M0(k_b - 7 - m), SFB_b = V scale byte;  l += sum_b (sum of the unquantised p of block b) * 2^(k_b - 7 - m)
 //   O = bf16(O_acc / l);  LSE = (m + log2 l) * ln2.  Key tiles are visited from the highest index down.
 //
-// CTA = one 128-query tile of one (batch, query head).  Warps 0-3: softmax / epilogue (thread t owns TMEM lane t = query
-// row t).  Warp 4: TMA producer.  Warp 5: MMA issuer and TMEM owner.  Every mbarrier wait is bounded.
+// Work item = one 128-query tile of one (batch, query head); a CTA walks a list of items.  Warps 0-3: softmax / epilogue
+// (thread t owns TMEM lane t = query row t).  Warp 4: TMA producer.  Warp 5: MMA issuer and TMEM owner.  Every mbarrier wait is bounded.
 #include <cstdlib>
 #include <type_traits>
 #include <cuda_bf16.h>
@@ -21,7 +21,6 @@ namespace dm {
 
 #ifdef DM_PROFILE
 // Tuning build only (-DDM_PROFILE): cycle counters of softmax warp 0 of the first CTA, read back with cudaMemcpyFromSymbol.
-__device__ long long g_fwd_prof[16];
 __device__ long long g_fwd1_prof[16];   // serial kernel
 __device__ long long g_fwd1_cta[4 * 1024];  // per CTA: start ns, end ns, tiles, SM id
 #define DM_PROF_T(var) const long long var = clock64()
@@ -377,303 +376,6 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
   if (warp == 5) tmem_dealloc(tmem, C::kTmemCols);
 }
 
-// ================================================================================================ pipelined (D = 128)
-// One CTA per SM, 576 threads.  Warps 0-15: four softmax groups of four warps; group g owns key block g (32 keys) of
-// every tile, i.e. one P scale block per thread and tile (thread t % 128 = query row = TMEM lane).  Warp 16: TMA.
-// Warp 17: MMA.  S is double-buffered in TMEM and the P codes / scale words have columns of their own (also double-
-// buffered), so the tensor pipe computes S of key tile i+1 and O += P V of tile i-1 behind the exponentials of tile i.
-// The four threads of a row agree on the running maximum once per tile through shared memory (they sit in four warps
-// of the same lane quadrant, hence of the same scheduler).
-struct FwdPipeCfg {
-  static constexpr int kTileBytes = 128 * 128;
-  static constexpr int kStages = 3;                      // K and V of a key tile share a stage
-  static constexpr int kGroups = 4;
-  static constexpr int kThreads = kGroups * 128 + 64;
-  static constexpr int kTmemCols = 512;
-  static constexpr int kColS = 0;                        // + 128 * buffer
-  static constexpr int kColO = 256;
-  static constexpr int kColP = 384;                      // + 32 * buffer: P codes, 8 columns per key block
-  static constexpr int kColX = 448;                      // + 16 * buffer: 4 x 4 columns, SFA word of key block g (byte 0)
-  static constexpr int kColSfb = 480;                    // + 4 * buffer: the tile's four V scale bytes
-  static constexpr int kSmemQ = 0;
-  static constexpr int kSmemK = kTileBytes;
-  static constexpr int kSmemV = kSmemK + kStages * kTileBytes;
-  static constexpr int kSmemXch = kSmemV + kStages * kTileBytes;       // 2 x [4 groups][128 rows] floats
-  static constexpr int kSmemBar = kSmemXch + 2 * 4 * 128 * 4;
-  static constexpr int kSmemBytes = kSmemBar + 256 + 1024;
-};
-
-__global__ void __launch_bounds__(FwdPipeCfg::kThreads, 1)
-fwd_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                const __grid_constant__ CUtensorMap tm_v, const FwdParams p) {
-  using C = FwdPipeCfg;
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* sQ = smem + C::kSmemQ;
-  uint8_t* sK = smem + C::kSmemK;
-  uint8_t* sV = smem + C::kSmemV;
-  float* sXch = reinterpret_cast<float*>(smem + C::kSmemXch);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kSmemBar);
-  uint64_t* bar_q = bars + 0;
-  uint64_t* bar_s = bars + 1;        // [2] S of the buffer ready (MMA commit)
-  uint64_t* bar_sfree = bars + 3;    // [2] every softmax warp holds its S columns (16 arrivals)
-  uint64_t* bar_p = bars + 5;        // [2] P codes and scale words of the buffer written (16 arrivals)
-  uint64_t* bar_pv = bars + 7;       // [2] the PV chain reading the buffer is done (MMA commit)
-  uint64_t* full = bars + 9;         // [kStages]
-  uint64_t* empty = bars + 12;       // [kStages]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 17);
-
-  const int tid = threadIdx.x, warp = tid >> 5;
-  const int n_qt = p.N / 128;
-  const int qt = n_qt - 1 - static_cast<int>(blockIdx.x);
-  const int bh = blockIdx.y;
-  const int b = bh / p.H, h = bh % p.H;
-  const int bhk = b * p.Hk + h / (p.H / p.Hk);
-  const int n_it = p.causal ? (qt + 1) : n_qt;
-  const int kt_first = p.causal ? qt : (n_qt - 1);          // key tiles are visited from the highest index down
-
-  if (tid == 0) {
-    mbar_init(bar_q, 1);
-    for (int s = 0; s < 2; ++s) {
-      mbar_init(bar_s + s, 1);
-      mbar_init(bar_sfree + s, C::kGroups * 4);
-      mbar_init(bar_p + s, C::kGroups * 4);
-      mbar_init(bar_pv + s, 1);
-    }
-    for (int s = 0; s < C::kStages; ++s) {
-      mbar_init(full + s, 1);
-      mbar_init(empty + s, 1);
-    }
-    *abort_flag = 0;
-    mbar_fence_init();
-  }
-  if (warp == 17) {
-    tmem_alloc(tmem_slot, C::kTmemCols);
-    tmem_relinquish();
-    tc_fence_before();
-  }
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem = *tmem_slot;
-
-  if (warp == 16) {
-    // ------------------------------------------------------------------------------------------ TMA producer
-    if (elect_one()) {
-      tma_prefetch_desc(&tm_q);
-      tma_prefetch_desc(&tm_k);
-      tma_prefetch_desc(&tm_v);
-      mbar_expect_tx(bar_q, C::kTileBytes);
-      tma_load_2d(sQ, &tm_q, bar_q, 0, bh * p.N + qt * 128);
-      for (int it = 0; it < n_it; ++it) {
-        const int st = it % C::kStages;
-        if (it >= C::kStages) {
-          if (!wait_or_abort(empty + st, ((it / C::kStages) - 1) & 1, abort_flag)) {
-            raise_abort(abort_flag, p.status, kStatusTimeoutProducer);
-            break;
-          }
-        }
-        const int row = bhk * p.N + (kt_first - it) * 128;
-        mbar_expect_tx(full + st, 2 * C::kTileBytes);
-        tma_load_2d(sK + st * C::kTileBytes, &tm_k, full + st, 0, row);
-        tma_load_2d(sV + st * C::kTileBytes, &tm_v, full + st, 0, row);
-      }
-    }
-  } else if (warp == 17) {
-    // ------------------------------------------------------------------------------------------ MMA issuer
-    if (elect_one()) {
-      constexpr uint32_t kIdescS = idesc_f8(128, 128, false, false);
-      const uint32_t q_lo = desc_lo(smem_u32(sQ)), k_lo0 = desc_lo(smem_u32(sK)), v_lo0 = desc_lo(smem_u32(sV));
-      auto issue_s = [&](int it) {
-        const uint32_t k_lo = k_lo0 + (it % C::kStages) * (C::kTileBytes >> 4);
-        const uint32_t t_s = tmem + C::kColS + 128 * (it & 1);
-#pragma unroll
-        for (int ks = 0; ks < 4; ++ks) mma_f8_ss(t_s, q_lo + ks * 2, k_lo + ks * 2, kIdescS, ks > 0);
-        tc_commit(bar_s + (it & 1));
-      };
-      bool ok = wait_or_abort(bar_q, 0, abort_flag);
-      if (ok) ok = wait_or_abort(full + 0, 0, abort_flag);
-      if (ok) {
-        tc_fence_after();
-        issue_s(0);
-      }
-      for (int it = 0; ok && it < n_it; ++it) {
-        const int st = it % C::kStages, buf = it & 1;
-        if (it + 1 < n_it) {
-          // S buffer of tile it+1 was last read for tile it-1
-          if (it >= 1 && !(ok = wait_or_abort(bar_sfree + (buf ^ 1), ((it - 1) >> 1) & 1, abort_flag))) break;
-          if (!(ok = wait_or_abort(full + (it + 1) % C::kStages, ((it + 1) / C::kStages) & 1, abort_flag))) break;
-          tc_fence_after();
-          issue_s(it + 1);
-        }
-        if (!(ok = wait_or_abort(bar_p + buf, (it >> 1) & 1, abort_flag))) break;
-        tc_fence_after();
-        // O += P V: A = P codes in TMEM (8 columns per 32-key step), B = V tile MN-major (32 key rows per step)
-        const uint32_t v_lo = v_lo0 + st * (C::kTileBytes >> 4);
-#pragma unroll
-        for (int ks = 0; ks < 4; ++ks)
-          mma_mxf8_ts(tmem + C::kColO, tmem + C::kColP + 32 * buf + ks * 8, v_lo + ks * 256,
-                      idesc_mxf8(128, 128, false, true, 0, ks), tmem + C::kColX + 16 * buf + 4 * ks,
-                      tmem + C::kColSfb + 4 * buf, (it > 0) || (ks > 0));
-        tc_commit(empty + st);
-        tc_commit(bar_pv + buf);
-      }
-      if (!ok) raise_abort(abort_flag, p.status, kStatusTimeoutMma);
-    }
-  } else {
-    // ------------------------------------------------------------------------------------------ softmax groups
-    const int wg = warp >> 2;                          // key block of every tile
-    const int quad = warp & 3;
-    const int r = tid & 127;                           // query row inside the tile = TMEM lane
-    const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
-    const int row = qt * 128 + r;
-    const int nblk = p.N / 32;
-    const float qsl = p.qs[static_cast<size_t>(bh) * nblk + row / 32] * kLog2e;
-    const float* ks_base = p.ks + static_cast<size_t>(bhk) * nblk + wg;
-    const float* vs_base = p.vs + static_cast<size_t>(bhk) * nblk;
-    float ks1 = ks_base[kt_first * 4];
-    float4 vs4 = *reinterpret_cast<const float4*>(vs_base + kt_first * 4);
-    float m = 0.f, l = 0.f;
-    bool ok = true;
-#ifdef DM_PROFILE
-    long long prof[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-#endif
-    for (int it = 0; it < n_it; ++it) {
-      const int kt = kt_first - it, buf = it & 1;
-      const float cb = qsl * ks1;
-      const uint32_t sfb = pack4(scale_to_sb(vs4.x), scale_to_sb(vs4.y), scale_to_sb(vs4.z), scale_to_sb(vs4.w));
-      if (it + 1 < n_it) {                             // scales of the next key tile, in flight during this one
-        ks1 = ks_base[(kt - 1) * 4];
-        if (wg == 0) vs4 = *reinterpret_cast<const float4*>(vs_base + (kt - 1) * 4);
-      }
-      const bool diag = p.causal && (kt == qt);
-      float bsum = 0.f, kb = 0.f;
-      float* xch = sXch + buf * 512;
-      DM_PROF_T(t0);
-      if (ok) ok = wait_warp(bar_s + buf, (it >> 1) & 1, abort_flag);
-      DM_PROF_T(t1);
-      DM_PROF_ADD(0, t0, t1);
-      if (ok) {
-        tc_fence_after();
-        uint32_t rs[32];
-        tmem_ld32(tmem + lane_base + C::kColS + 128 * buf + 32 * wg, rs);
-        tmem_wait_ld();
-        tc_fence_before();
-        __syncwarp();
-        if ((tid & 31) == 0) mbar_arrive(bar_sfree + buf);
-        DM_PROF_T(t2);
-        DM_PROF_ADD(1, t1, t2);
-        if (diag) {
-#pragma unroll
-          for (int e = 0; e < 32; ++e)
-            if (32 * wg + e > r) rs[e] = 0xff800000u;            // -inf: key index above the query index
-        }
-        float2 s2[16];
-#pragma unroll
-        for (int e = 0; e < 16; ++e) s2[e] = make_float2(__uint_as_float(rs[2 * e]), __uint_as_float(rs[2 * e + 1]));
-        const float bmax = max32(s2) * cb;
-        xch[wg * 128 + r] = bmax;                      // this block's contribution to the row maximum
-        kb = fmaxf(floorf(bmax), -1e30f);
-        const float2 c2 = splat2(cb), bias2 = splat2(7.0f - kb);
-        float2 sum0 = make_float2(0.f, 0.f), sum1 = sum0;
-        uint32_t codes[8];
-#pragma unroll
-        for (int e = 0; e < 16; e += 2) {
-          const float2 p0 = ex2_2(fma2(s2[e], c2, bias2));
-          const float2 p1 = ex2_2(fma2(s2[e + 1], c2, bias2));
-          sum0 = add2(sum0, p0);
-          sum1 = add2(sum1, p1);
-          codes[e / 2] = cvt_e4m3x4(p0.x, p0.y, p1.x, p1.y);
-        }
-        sum0 = add2(sum0, sum1);
-        bsum = sum0.x + sum0.y;
-        DM_PROF_T(t3);
-        DM_PROF_ADD(2, t2, t3);
-        // the PV chain of tile it-2 read this code / scale-word buffer
-        if (it >= 2) ok = wait_warp(bar_pv + buf, ((it - 2) >> 1) & 1, abort_flag);
-        DM_PROF_T(t4);
-        DM_PROF_ADD(3, t3, t4);
-        if (ok) tmem_st8(tmem + lane_base + C::kColP + 32 * buf + 8 * wg, codes);
-      }
-      DM_PROF_T(t5);
-      bar_sync(1 + quad, 128);       // the four warps of this lane quadrant: reached in every iteration, also after a failed wait
-      DM_PROF_T(t6);
-      DM_PROF_ADD(4, t5, t6);
-      if (!ok) continue;
-      const float mcand = ceilf(fmaxf(fmaxf(xch[r], xch[128 + r]), fmaxf(xch[256 + r], xch[384 + r])));
-      float acc_scale = 1.0f;
-      if (it == 0) {
-        m = mcand;
-      } else if (mcand > m + 32.0f) {
-        acc_scale = sb_to_scale(static_cast<uint32_t>(max(0, min(__float2int_rn(m - mcand) + 127, 254))));
-        m = mcand;
-      }
-      if (it > 0 && __any_sync(0xffffffffu, acc_scale != 1.0f)) {
-        // rare: the running maximum moved by more than 32 binades; rescale this thread's 32 O columns in place, after
-        // the PV chain of the previous tile has finished accumulating into them
-        ok = wait_warp(bar_pv + (buf ^ 1), ((it - 1) >> 1) & 1, abort_flag);
-        if (!ok) continue;
-        tc_fence_after();
-        uint32_t ro[32];
-        tmem_ld32(tmem + lane_base + C::kColO + 32 * wg, ro);
-        tmem_wait_ld();
-#pragma unroll
-        for (int e = 0; e < 32; ++e) ro[e] = __float_as_uint(__uint_as_float(ro[e]) * acc_scale);
-        tmem_st32(tmem + lane_base + C::kColO + 32 * wg, ro);
-      }
-      const int e = __float2int_rn(kb - 7.0f - m);           // saturates for fully masked blocks
-      const uint32_t sb = static_cast<uint32_t>(max(0, min(max(e, -1000) + 127, 254)));
-      l = fmaf(bsum, __uint_as_float(sb << 23), l * acc_scale);
-      tmem_st4(tmem + lane_base + C::kColX + 16 * buf + 4 * wg, sb, sb, sb, sb);
-      if (wg == 0) tmem_st4(tmem + lane_base + C::kColSfb + 4 * buf, sfb, sfb, sfb, sfb);
-      DM_PROF_T(t7);
-      tmem_wait_st();
-      DM_PROF_T(t8);
-      DM_PROF_ADD(6, t7, t8);
-      tc_fence_before();
-      __syncwarp();
-      if ((tid & 31) == 0) mbar_arrive(bar_p + buf);
-      DM_PROF_T(t9);
-      DM_PROF_ADD(5, t6, t9);
-    }
-#ifdef DM_PROFILE
-    if (blockIdx.x == 0 && blockIdx.y == 0 && tid == 0) {
-      for (int i = 0; i < 8; ++i) g_fwd_prof[i] = prof[i];
-      g_fwd_prof[8] = n_it;
-    }
-#endif
-    if (ok) ok = wait_warp(bar_pv + ((n_it - 1) & 1), ((n_it - 1) >> 1) & 1, abort_flag);
-    if (!ok) raise_abort(abort_flag, p.status, kStatusTimeoutCompute);
-    // the row sum: the four groups' partial sums (taken against the common running maximum) meet in shared memory
-    float* xl = sXch + ((n_it & 1) ? 512 : 0);         // the buffer the last tile did not use
-    xl[wg * 128 + r] = l;
-    bar_sync(1 + quad, 128);
-    if (ok) {
-      const float lt = ((xl[r] + xl[128 + r]) + xl[256 + r]) + xl[384 + r];
-      tc_fence_after();
-      const float inv_l = 1.0f / lt;
-      uint32_t ro[32];
-      tmem_ld32(tmem + lane_base + C::kColO + 32 * wg, ro);
-      tmem_wait_ld();
-      __nv_bfloat16* dst = p.o + static_cast<int64_t>(b) * p.o_sb + static_cast<int64_t>(row) * p.o_sn +
-                           static_cast<int64_t>(h) * p.o_sh + 32 * wg;
-      uint32_t w[16];
-#pragma unroll
-      for (int e2 = 0; e2 < 16; ++e2) {
-        __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(ro[2 * e2]) * inv_l, __uint_as_float(ro[2 * e2 + 1]) * inv_l);
-        w[e2] = *reinterpret_cast<uint32_t*>(&v);
-      }
-      uint4* d4 = reinterpret_cast<uint4*>(dst);
-#pragma unroll
-      for (int e2 = 0; e2 < 4; ++e2) d4[e2] = make_uint4(w[4 * e2], w[4 * e2 + 1], w[4 * e2 + 2], w[4 * e2 + 3]);
-      if (wg == 0) p.lse[static_cast<size_t>(bh) * p.N + row] = (m + log2f(lt)) * kLn2;
-    }
-  }
-  tc_fence_before();
-  __syncthreads();
-  if (warp == 17) tmem_dealloc(tmem, C::kTmemCols);
-}
-
 template <int D>
 static cudaError_t launch_fwd_t(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FwdParams& p,
                                 cudaStream_t stream) {
@@ -705,34 +407,13 @@ extern "C" int dm_prof_read_fwd1_cta(long long* host4096) {
 extern "C" int dm_prof_read_fwd1(long long* host16) {
   return static_cast<int>(cudaMemcpyFromSymbol(host16, dm::g_fwd1_prof, sizeof(long long) * 16));
 }
-extern "C" int dm_prof_read_fwd(long long* host16) {
-  return static_cast<int>(cudaMemcpyFromSymbol(host16, g_fwd_prof, sizeof(long long) * 16));
-}
 #endif
 
 cudaError_t launch_fwd(int D, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FwdParams& p,
                        cudaStream_t stream) {
-  // head_dim 256: S double-buffered plus a 256-column O fill the 512 TMEM columns, which leaves no room for separate P
-  // code and scale-word columns; it keeps the kernel that serialises MMA and softmax inside a CTA.
+  // One kernel for both head dims: S (128 columns) plus O (head_dim columns) per CTA, two CTAs per SM at head_dim 128.
   if (D != 128) return launch_fwd_t<256>(tq, tk, tv, p, stream);
-  // DM_FWD_PIPE=1 (tuning) selects the one-CTA-per-SM pipelined kernel; measured on B200 at B=4 N=4096 H=32 it takes
-  // 0.76 ms against 0.66 ms for two co-resident CTAs of the serialised kernel, whose latencies hide each other.
-  static const bool pipe = [] {
-    const char* e = getenv("DM_FWD_PIPE");
-    return e != nullptr && e[0] == '1';
-  }();
-  if (!pipe) return launch_fwd_t<128>(tq, tk, tv, p, stream);
-  static bool attr_set[64] = {};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(fwd_pipe_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdPipeCfg::kSmemBytes);
-    if (e != cudaSuccess) return e;
-    attr_set[dev] = true;
-  }
-  dim3 grid(p.N / 128, p.B * p.H);
-  fwd_pipe_kernel<<<grid, FwdPipeCfg::kThreads, FwdPipeCfg::kSmemBytes, stream>>>(tq, tk, tv, p);
-  return cudaGetLastError();
+  return launch_fwd_t<128>(tq, tk, tv, p, stream);
 }
 
 }  // namespace dm
