@@ -22,13 +22,12 @@ namespace dm {
 
 struct DqP2Cfg {
   static constexpr int kTileBytes = 128 * 128;
-  static constexpr int kStages = 5;            // dS^T tile + K tile per stage
+  static constexpr int kStages = 7;            // dS^T tile + K tile + scale word per stage (7 x 32 KiB of the 227 KiB)
   static constexpr int kThreads = 320;
   static constexpr int kTmemCols = 512;
   static constexpr int kColDq = 0;             // 2 x 128 fp32 columns
-  static constexpr int kSf = 4;                // scale-word buffers (tiles the scale warps may run ahead of the MMAs)
-  static constexpr int kColSf = 256;           // kSf x 4 columns: the tile's scale word
-  static constexpr int kColOne = 256 + 4 * kSf;   // 4 columns of 0x7F7F7F7F: scale 1.0 for the B operand
+  static constexpr int kColSf = 256;           // kStages x 4 columns: the tile's scale word
+  static constexpr int kColOne = 256 + 4 * kStages;   // 4 columns of 0x7F7F7F7F: scale 1.0 for the B operand
   static constexpr int kSmemDs = 0;
   static constexpr int kSmemK = kStages * kTileBytes;
   static constexpr int kSmemBar = 2 * kStages * kTileBytes;
@@ -43,14 +42,16 @@ bwd_dq_p2_kernel(const __grid_constant__ CUtensorMap tm_ds, const __grid_constan
   uint8_t* sDs = smem + C::kSmemDs;
   uint8_t* sK = smem + C::kSmemK;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kSmemBar);
-  uint64_t* full = bars + 0;          // [kStages] both tiles of the stage landed
-  uint64_t* empty = bars + 5;         // [kStages] the stage's chain has read them (MMA commit)
-  uint64_t* sf_full = bars + 10;      // [kSf] scale word of the tile written (one arrival per scale warp)
-  uint64_t* sf_free = bars + 14;      // [kSf] the chain that read the word is done (MMA commit)
-  uint64_t* dq_full = bars + 18;      // [2] last chain of the item done (MMA commit)
-  uint64_t* dq_free = bars + 20;      // [2] accumulator read out (one arrival per epilogue warp)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 22);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 23);
+  // One barrier pair per stage keeps the MMA thread's loop short (one wait, four MMAs, one commit per tile): `full`
+  // collects the TMA transaction and one arrival per scale warp, `empty` (MMA commit) releases the stage's shared memory
+  // to the TMA warp and its scale-word columns to the scale warps.
+  uint64_t* full = bars + 0;          // [kStages] tiles landed and scale word written
+  uint64_t* empty = bars + C::kStages;          // [kStages] the stage's chain has read them (MMA commit)
+  uint64_t* dq_full = bars + 2 * C::kStages;     // [2] last chain of the item done (MMA commit)
+  uint64_t* dq_free = bars + 2 * C::kStages + 2; // [2] accumulator read out (one arrival per epilogue warp)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * C::kStages + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 2 * C::kStages + 5);
+  static_assert(2 * C::kStages + 6 <= 32, "barrier block is 256 bytes");
 
   const int tid = threadIdx.x, warp = tid >> 5;
   const int n_t = p.N / 128;
@@ -62,12 +63,8 @@ bwd_dq_p2_kernel(const __grid_constant__ CUtensorMap tm_ds, const __grid_constan
 
   if (tid == 0) {
     for (int s = 0; s < C::kStages; ++s) {
-      mbar_init(full + s, 1);
+      mbar_init(full + s, 1 + 4);
       mbar_init(empty + s, 1);
-    }
-    for (int s = 0; s < C::kSf; ++s) {
-      mbar_init(sf_full + s, 4);
-      mbar_init(sf_free + s, 1);
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(dq_full + s, 1);
@@ -120,9 +117,8 @@ bwd_dq_p2_kernel(const __grid_constant__ CUtensorMap tm_ds, const __grid_constan
         // the accumulator was last used two items ago: its read-out must be complete
         if (n_done >= 2 && !(ok = wait_or_abort(dq_free + acc, ((n_done >> 1) - 1) & 1, abort_flag))) break;
         for (int it = 0; it < n_it; ++it, ++g) {
-          const uint32_t st = g % C::kStages, sf = g % C::kSf;
+          const uint32_t st = g % C::kStages;
           if (!(ok = wait_or_abort(full + st, (g / C::kStages) & 1, abort_flag))) break;
-          if (!(ok = wait_or_abort(sf_full + sf, (g / C::kSf) & 1, abort_flag))) break;
           tc_fence_after();
           // dQ += dS K over the tile's 128 keys: A = dS^T tile read MN-major, B = K tile read MN-major; both advance
           // by 32 key rows (4096 bytes) per step; byte ks of the scale word belongs to key block ks
@@ -130,10 +126,9 @@ bwd_dq_p2_kernel(const __grid_constant__ CUtensorMap tm_ds, const __grid_constan
 #pragma unroll
           for (int ks = 0; ks < 4; ++ks)
             mma_mxf8_ss(tmem + C::kColDq + 128 * acc, ds_lo + ks * 256, k_lo + ks * 256,
-                        idesc_mxf8(128, 128, true, true, ks, 0), tmem + C::kColSf + 4 * sf, tmem + C::kColOne,
+                        idesc_mxf8(128, 128, true, true, ks, 0), tmem + C::kColSf + 4 * st, tmem + C::kColOne,
                         (it > 0) || (ks > 0));
           tc_commit(empty + st);
-          tc_commit(sf_free + sf);
           if (it == n_it - 1) tc_commit(dq_full + acc);
         }
       }
@@ -201,14 +196,14 @@ bwd_dq_p2_kernel(const __grid_constant__ CUtensorMap tm_ds, const __grid_constan
         }
         const uint32_t word = pack4(sb_mul(w & 0xFF, scale_to_sb(k4.x)), sb_mul((w >> 8) & 0xFF, scale_to_sb(k4.y)),
                                     sb_mul((w >> 16) & 0xFF, scale_to_sb(k4.z)), sb_mul(w >> 24, scale_to_sb(k4.w)));
-        const uint32_t sf = g % C::kSf;
-        if (g >= C::kSf && !(ok = wait_warp(sf_free + sf, ((g / C::kSf) - 1) & 1, abort_flag))) break;
+        const uint32_t st = g % C::kStages;
+        if (g >= C::kStages && !(ok = wait_warp(empty + st, ((g / C::kStages) - 1) & 1, abort_flag))) break;
         tc_fence_after();
-        tmem_st4(tmem + lane_base + C::kColSf + 4 * sf, word, word, word, word);
+        tmem_st4(tmem + lane_base + C::kColSf + 4 * st, word, word, word, word);
         tmem_wait_st();
         tc_fence_before();
         __syncwarp();
-        if ((tid & 31) == 0) mbar_arrive(sf_full + sf);
+        if ((tid & 31) == 0) mbar_arrive(full + st);
       }
     }
     if (!ok) raise_abort(abort_flag, p.status, kStatusTimeoutCompute);

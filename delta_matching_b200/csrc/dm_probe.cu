@@ -113,7 +113,7 @@ probe_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
 // everything about the MMA fixed at compile time so that the issue path is as short as in the attention kernels.
 // cycles[0] = first issue -> completion seen through the commit mbarrier, [1] = issue only, [2] = one
 // tcgen05.ld.32x32b.x32 + wait::ld in a compute warp, [3] = one MMA + commit -> completion (round trip).
-template <int N, bool SCALED, bool ATMEM, bool BMN>
+template <int N, bool SCALED, bool ATMEM, bool BMN, bool AMN = false>
 __global__ void __launch_bounds__(128, 1)
 mma_cycles_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b, int* status,
                   int repeat, unsigned long long* cycles) {
@@ -175,8 +175,8 @@ mma_cycles_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
             if (SCALED) {
               if (ATMEM) mma_mxf8_ts(tmem + kColD, tmem + kColA + ks * 8, db, idesc_mxf8(128, N, false, BMN, ks, ks),
                                      tmem + kColSfa, tmem + kColSfb, acc);
-              else mma_mxf8_ss(tmem + kColD, a_lo + ks * 2, db, idesc_mxf8(128, N, false, BMN, ks, ks), tmem + kColSfa,
-                               tmem + kColSfb, acc);
+              else mma_mxf8_ss(tmem + kColD, a_lo + (AMN ? ks * 256 : ks * 2), db, idesc_mxf8(128, N, AMN, BMN, ks, ks),
+                               tmem + kColSfa, tmem + kColSfb, acc);
             } else {
               if (ATMEM) mma_f8_ts(tmem + kColD, tmem + kColA + ks * 8, db, idesc_f8(128, N, false, BMN), acc);
               else mma_f8_ss(tmem + kColD, a_lo + ks * 2, db, idesc_f8(128, N, false, BMN), acc);
@@ -224,14 +224,14 @@ mma_cycles_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   if (warp == 0) tmem_dealloc(tmem, 512);
 }
 
-template <int N, bool SCALED, bool ATMEM, bool BMN>
+template <int N, bool SCALED, bool ATMEM, bool BMN, bool AMN = false>
 static cudaError_t launch_cycles_t(const CUtensorMap& ta, const CUtensorMap& tb, int* status, int repeat,
                                    unsigned long long* cycles, cudaStream_t stream) {
   constexpr int kSmem = 32768 + 64 + 1024;
-  cudaError_t e = cudaFuncSetAttribute(mma_cycles_kernel<N, SCALED, ATMEM, BMN>,
+  cudaError_t e = cudaFuncSetAttribute(mma_cycles_kernel<N, SCALED, ATMEM, BMN, AMN>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
   if (e != cudaSuccess) return e;
-  mma_cycles_kernel<N, SCALED, ATMEM, BMN><<<1, 128, kSmem, stream>>>(ta, tb, status, repeat, cycles);
+  mma_cycles_kernel<N, SCALED, ATMEM, BMN, AMN><<<1, 128, kSmem, stream>>>(ta, tb, status, repeat, cycles);
   return cudaGetLastError();
 }
 
@@ -239,8 +239,9 @@ static cudaError_t launch_cycles_t(const CUtensorMap& ta, const CUtensorMap& tb,
 // memory and an MN-major B (PV, dV, dK, dQ), at widths 128 and 64.
 cudaError_t launch_mma_cycles(const CUtensorMap& ta, const CUtensorMap& tb, const ProbeParams& p, int n_cols, int repeat,
                               unsigned long long* cycles, cudaStream_t stream) {
-  const int key = (n_cols == 128 ? 0 : 1) | (p.scaled ? 2 : 0) | (p.a_tmem ? 4 : 0) | (p.b_mn ? 8 : 0);
+  const int key = (n_cols == 128 ? 0 : 1) | (p.scaled ? 2 : 0) | (p.a_tmem ? 4 : 0) | (p.b_mn ? 8 : 0) | (p.a_mn ? 16 : 0);
   switch (key) {
+    case 16 | 8 | 2: return launch_cycles_t<128, true, false, true, true>(ta, tb, p.status, repeat, cycles, stream);
     case 0: return launch_cycles_t<128, false, false, false>(ta, tb, p.status, repeat, cycles, stream);
     case 1: return launch_cycles_t<64, false, false, false>(ta, tb, p.status, repeat, cycles, stream);
     case 8 | 4 | 2: return launch_cycles_t<128, true, true, true>(ta, tb, p.status, repeat, cycles, stream);
