@@ -609,7 +609,7 @@ bwd_dkdv_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           float pm0 = 0.f, pm1 = 0.f;
 #pragma unroll
           for (int e = 0; e < 16; e += 2) {
-            const float4 l4 = *reinterpret_cast<const float4*>(lse_s + 32 * c + 2 * e);
+            const float4 l4 = lds_f4(lse_s + 32 * c + 2 * e);
             const float2 x0 = fma2(make_float2(__uint_as_float(rs[c][2 * e]), __uint_as_float(rs[c][2 * e + 1])), cc,
                                    mul2(make_float2(l4.x, l4.y), nlog2e));
             const float2 x1 = fma2(make_float2(__uint_as_float(rs[c][2 * e + 2]), __uint_as_float(rs[c][2 * e + 3])), cc,
@@ -667,7 +667,7 @@ bwd_dkdv_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           const float2 naa = splat2(-(vs_row * dos_c[c]));
 #pragma unroll
           for (int e = 0; e < 16; e += 2) {
-            const float4 d4 = *reinterpret_cast<const float4*>(dl_s + 32 * c + 2 * e);
+            const float4 d4 = lds_f4(dl_s + 32 * c + 2 * e);
             const float2 t0 = fma2(make_float2(__uint_as_float(rd[c][2 * e]), __uint_as_float(rd[c][2 * e + 1])), naa,
                                    make_float2(d4.x, d4.y));
             const float2 t1 = fma2(make_float2(__uint_as_float(rd[c][2 * e + 2]), __uint_as_float(rd[c][2 * e + 3])), naa,
@@ -716,8 +716,8 @@ bwd_dkdv_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           // chunk j ^ (r % 8)); the MMA warp's thread stores the tile to the workspace for pass 2
           uint8_t* ws_row = sWs + ph * C::kTileBytes + r * 128;
           const int j = 2 * (blk0 + c);
-          *reinterpret_cast<uint4*>(ws_row + ((j ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
-          *reinterpret_cast<uint4*>(ws_row + (((j + 1) ^ (r & 7)) << 4)) = make_uint4(w[4], w[5], w[6], w[7]);
+          sts_u4(ws_row + ((j ^ (r & 7)) << 4), w[0], w[1], w[2], w[3]);
+          sts_u4(ws_row + (((j + 1) ^ (r & 7)) << 4), w[4], w[5], w[6], w[7]);
         }
       }
       if (p.ds_codes != nullptr) fence_async_smem();
@@ -1279,8 +1279,8 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         codes32(v, sb_to_inv(dsb), w);
         // row r of the dS tile: 16-byte chunk j of the row lands at chunk (j ^ (r % 8)) (128-byte swizzle)
         uint8_t* ds_row = sDs + (g & 1) * C::kTileBytes + r * 128;
-        *reinterpret_cast<uint4*>(ds_row + (((2 * wg) ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
-        *reinterpret_cast<uint4*>(ds_row + (((2 * wg + 1) ^ (r & 7)) << 4)) = make_uint4(w[4], w[5], w[6], w[7]);
+        sts_u4(ds_row + (((2 * wg) ^ (r & 7)) << 4), w[0], w[1], w[2], w[3]);
+        sts_u4(ds_row + (((2 * wg + 1) ^ (r & 7)) << 4), w[4], w[5], w[6], w[7]);
         const uint32_t word = sb_mul(dsb, scale_to_sb(ksv));
         tmem_st4(tmem + lane_base + C::kColX + 4 * wg, word, word, word, word);
         if (wg == 0) tmem_st4(tmem + lane_base + C::kColOne, 0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu);
