@@ -5,6 +5,7 @@
 // Numerics follow the reference's Blackwell contract ("sm100-mx"): delta_matching/reference.py:159-171 (mx_pfwd),
 // :454-471 (forward engine) and the op list in delta_matching/sm100/dm_fwd_sm100.py:3685-3757:
 //   c_b = (qs * log2e) * ks_b;  xb = max_b(S_acc) * c_b;  k_b = max(floor(xb), -1e30);  p = ex2(fma(S_acc, c_b, 7 - k_b))
+//   (ex2 = ex2.approx, or a polynomial of the same accuracy on the FMA pipe for three of sixteen element pairs)
 //   code = e4m3(p);  m integer-valued running max (ceil), moved only when the candidate exceeds it by more than 32;
 //   SFA_b = UE8M0(k_b - 7 - m), SFB_b = V scale byte;  l += sum_b (sum of the unquantised p of block b) * 2^(k_b - 7 - m)
 //   O = bf16(O_acc / l);  LSE = (m + log2 l) * ln2.  Key tiles are visited from the highest index down.
@@ -269,7 +270,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
 #pragma unroll
           for (int e = 0; e < 16; e += 2) {
             const float2 p0 = ex2_2(fma2(s2[e], c2, bias2));
-            const float2 p1 = ex2_2(fma2(s2[e + 1], c2, bias2));
+            // three of the sixteen pairs take the polynomial: the MUFU pipe is the floor of this loop, the FMA pipe has room
+            const float2 p1 = (e == 2 || e == 8 || e == 14) ? ex2_poly2(fma2(s2[e + 1], c2, bias2)) : ex2_2(fma2(s2[e + 1], c2, bias2));
             sum0 = add2(sum0, p0);
             sum1 = add2(sum1, p1);
             codes[e / 2] = cvt_e4m3x4(p0.x, p0.y, p1.x, p1.y);

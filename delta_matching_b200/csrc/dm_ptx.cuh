@@ -296,6 +296,24 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
   asm("max.f32 %0, %1, %2, %3;" : "=f"(m) : "f"(a), "f"(b), "f"(c));
   return m;
 }
+// 2^x on the FMA and integer pipes for a part of the exponentials (the MUFU pipe, 16 results per clock and SM, is the
+// floor of the attention kernels): round-to-nearest split x = n + f with f in [-0.5, 0.5] through the 1.5 * 2^23 trick,
+// degree-5 polynomial for 2^f (2.4e-7 relative error in fp32, the accuracy of ex2.approx), n added to the exponent field.
+// Arguments below -120 are clamped (the result, < 1e-36, is zero for every use here); arguments must stay below 120.
+__device__ __forceinline__ float2 ex2_poly2(float2 x) {
+  x = make_float2(fmaxf(x.x, -120.0f), fmaxf(x.y, -120.0f));
+  const float2 big = splat2(12582912.0f);
+  const float2 t = add2(x, big);
+  const float2 n = add2(t, splat2(-12582912.0f));
+  const float2 f = add2(x, make_float2(-n.x, -n.y));
+  float2 q = fma2(f, splat2(0.0013390863314270973f), splat2(0.009676031768321991f));
+  q = fma2(q, f, splat2(0.055503569543361664f));
+  q = fma2(q, f, splat2(0.2402210682630539f));
+  q = fma2(q, f, splat2(0.6931471824645996f));
+  q = fma2(q, f, splat2(1.0000001192092896f));
+  return make_float2(__uint_as_float(__float_as_uint(q.x) + (__float_as_uint(t.x) << 23)),
+                     __uint_as_float(__float_as_uint(q.y) + (__float_as_uint(t.y) << 23)));
+}
 // max over 32 floats held as 16 pairs (exact, order-free)
 __device__ __forceinline__ float max32(const float2 (&v)[16]) {
   float m0 = max3(v[0].x, v[0].y, v[1].x), m1 = max3(v[1].y, v[2].x, v[2].y);
