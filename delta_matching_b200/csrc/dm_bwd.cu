@@ -539,6 +539,7 @@ bwd_dkdv_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     const float ks_row = p.ks[static_cast<size_t>(bhk) * nblk + key / 32];
     const float vs_row = p.vs[static_cast<size_t>(bhk) * nblk + key / 32];
     const float2 nlog2e = splat2(-kLog2e);
+    const uint32_t vec_a = smem_u32(sVec), xch_a = smem_u32(sXch), ws_a = smem_u32(sWs);
     bool ok = true;
     // iteration state kept incrementally: stage and its phase, query tile, and the scale pointers of (head, tile)
     int st = 0, qi = 0;
@@ -578,8 +579,8 @@ bwd_dkdv_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           }
         }
       }
-      const float* lse_s = sVec + st * 256 + 32 * blk0;
-      const float* dl_s = lse_s + 128;
+      const uint32_t lse_a = vec_a + st * 1024 + 128 * blk0;       // shared-window addresses of lse / delta of the stage
+      const uint32_t dl_a = lse_a + 512;
       float2 pr[CH][16];
       DM_PROF_T(t0);
       if (ok) ok = wait_warp(full + st, st_ph, abort_flag);       // lse / delta of the tile are in smem
@@ -609,7 +610,7 @@ bwd_dkdv_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           float pm0 = 0.f, pm1 = 0.f;
 #pragma unroll
           for (int e = 0; e < 16; e += 2) {
-            const float4 l4 = lds_f4(lse_s + 32 * c + 2 * e);
+            const float4 l4 = lds_f4(lse_a + 4 * (32 * c + 2 * e));
             const float2 x0 = fma2(make_float2(__uint_as_float(rs[c][2 * e]), __uint_as_float(rs[c][2 * e + 1])), cc,
                                    mul2(make_float2(l4.x, l4.y), nlog2e));
             const float2 x1 = fma2(make_float2(__uint_as_float(rs[c][2 * e + 2]), __uint_as_float(rs[c][2 * e + 3])), cc,
@@ -667,7 +668,7 @@ bwd_dkdv_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           const float2 naa = splat2(-(vs_row * dos_c[c]));
 #pragma unroll
           for (int e = 0; e < 16; e += 2) {
-            const float4 d4 = lds_f4(dl_s + 32 * c + 2 * e);
+            const float4 d4 = lds_f4(dl_a + 4 * (32 * c + 2 * e));
             const float2 t0 = fma2(make_float2(__uint_as_float(rd[c][2 * e]), __uint_as_float(rd[c][2 * e + 1])), naa,
                                    make_float2(d4.x, d4.y));
             const float2 t1 = fma2(make_float2(__uint_as_float(rd[c][2 * e + 2]), __uint_as_float(rd[c][2 * e + 3])), naa,
@@ -679,7 +680,7 @@ bwd_dkdv_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           }
         }
         const float wm = warp_max(fmaxf(am0, am1));
-        if ((tid & 31) == 0) sXch[ph * 16 + warp] = wm;
+        if ((tid & 31) == 0) sts_f(xch_a + 4 * (ph * 16 + warp), wm);
         DM_PROF_T(t9);
         DM_PROF_ADD(7, t8, t9);
       }
@@ -699,9 +700,9 @@ bwd_dkdv_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       DM_PROF_T(t11);
       DM_PROF_ADD(8, t10, t11);
       if (!ok) continue;
-      const float* x = sXch + ph * 16 + quad;
-      float am = fmaxf(x[0], x[4]);
-      if (C::kGroups == 4) am = fmaxf(am, fmaxf(x[8], x[12]));
+      const uint32_t x_a = xch_a + 4 * (ph * 16 + quad);
+      float am = fmaxf(lds_f(x_a), lds_f(x_a + 16));
+      if (C::kGroups == 4) am = fmaxf(am, fmaxf(lds_f(x_a + 32), lds_f(x_a + 48)));
       const uint32_t dsb = pow2_sb(am, 127u);
       const float ninv = -sb_to_inv(dsb);
 #pragma unroll
@@ -714,7 +715,7 @@ bwd_dkdv_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         if (p.ds_codes != nullptr) {
           // the same codes as a [key][query] tile in 128-byte-swizzled shared memory (16-byte chunk j of row r at
           // chunk j ^ (r % 8)); the MMA warp's thread stores the tile to the workspace for pass 2
-          uint8_t* ws_row = sWs + ph * C::kTileBytes + r * 128;
+          const uint32_t ws_row = ws_a + ph * C::kTileBytes + r * 128;
           const int j = 2 * (blk0 + c);
           sts_u4(ws_row + ((j ^ (r & 7)) << 4), w[0], w[1], w[2], w[3]);
           sts_u4(ws_row + (((j + 1) ^ (r & 7)) << 4), w[4], w[5], w[6], w[7]);
