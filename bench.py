@@ -173,10 +173,33 @@ def run_reference(args, w, rank):
             "cpu_baseline": {"value": tf, "unit": "TFLOPS", "cores": cores, "kind": "port", "sample": sample},
             "e2e": {"value": tf, "unit": "TFLOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
-    print(json.dumps(line), flush=True)
+    emit(line)
+
+
+_RESULT_FD = None
+
+
+def own_stdout():
+    """Libraries (NCCL's version banner, build tools) write to file descriptor 1; the contract is one JSON line there.  Keep
+    a private duplicate of the real stdout for that line and point descriptor 1 at stderr for everything else."""
+    global _RESULT_FD
+    if _RESULT_FD is None:
+        sys.stdout.flush()
+        _RESULT_FD = os.dup(1)
+        os.dup2(2, 1)
+
+
+def emit(line):
+    data = (json.dumps(line) + "\n").encode()
+    if _RESULT_FD is None:
+        sys.stdout.write(data.decode())
+        sys.stdout.flush()
+    else:
+        os.write(_RESULT_FD, data)
 
 
 def main():
+    own_stdout()
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=30)
@@ -328,7 +351,7 @@ def main():
             tf, cms, cores, sample = cpu_sample(w)
             line["cpu_baseline"] = {"value": tf, "unit": "TFLOPS", "cores": cores, "kind": "port", "sample": sample,
                                     "ms_per_sample": cms}
-        print(json.dumps(line), flush=True)
+        emit(line)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
