@@ -3,8 +3,8 @@
 `attn_step_host` takes pinned CPU tensors, splits the batch into chunks (the (batch, head) problems are independent, so
 the results are bit-identical to one un-chunked call) and runs three streams: host->device copies of chunk c + 1,
 kernels of chunk c and device->host copies of chunk c - 1 overlap, which hides the compute and one direction of the
-PCIe traffic behind the other.  Everything on the device goes through `dm_attn_func` and autograd, i.e. the same path
-as a call with CUDA tensors (reference surface: delta_matching/__init__.py:52-77).
+PCIe traffic behind the other.  The device work is the op sequence of `dm_attn_func` and its backward
+(delta_matching_b200/attn.py; reference surface: delta_matching/__init__.py:52-77), with the same input checks.
 """
 from __future__ import annotations
 
@@ -39,8 +39,13 @@ def attn_step_host(q, k, v, do, *, causal=True, mode="matched", softmax_scale=No
     q, do: (B, N, H, D); k, v: (B, N, Hk, D); bf16, contiguous, pinned.  Returns (o, dq, dk, dv) as pinned CPU tensors
     (or fills `out`, a tuple of four such tensors).  The copies are asynchronous: the results are complete once the
     current CUDA stream of `device` has been synchronised.  `chunks` (default: the batch size) is how many slices of
-    the batch are pipelined; argument errors are those of `dm_attn_func`."""
-    from . import dm_attn_func
+    the batch are pipelined; argument errors are those of `dm_attn_func`.
+
+    Per chunk: q, k, v are copied in and the forward starts while dO is still on its way; O is copied out while the
+    backward runs; dQ, dK, dV follow.  The kernels are the ones `dm_attn_func` and its backward launch, in the same
+    order (the op layer is called directly, there is no autograd graph)."""
+    from . import ops
+    from .attn import _check_inputs
     for name, t in (("q", q), ("k", k), ("v", v), ("do", do)):
         _check_host(name, t)
     if do.shape != q.shape:
@@ -62,12 +67,13 @@ def attn_step_host(q, k, v, do, *, causal=True, mode="matched", softmax_scale=No
     bounds = [(B * c) // n_chunks for c in range(n_chunks + 1)]
     per = max(bounds[c + 1] - bounds[c] for c in range(n_chunks))
 
-    with torch.cuda.device(dev):
+    with torch.cuda.device(dev), torch.no_grad():
         main = torch.cuda.current_stream(dev)
         s_in, s_out = _side_streams(dev)
         # two sets of device input buffers, allocated on the main stream
         bufs = [[torch.empty((per,) + tuple(t.shape[1:]), dtype=torch.bfloat16, device=dev) for t in (q, k, v, do)]
                 for _ in range(min(2, n_chunks))]
+        _check_inputs(*(t[:1].transpose(1, 2) for t in bufs[0][:3]), causal, softmax_scale, mode)
         start = torch.cuda.Event()
         start.record(main)
         s_in.wait_event(start)
@@ -76,25 +82,43 @@ def attn_step_host(q, k, v, do, *, causal=True, mode="matched", softmax_scale=No
         last_out = None
         for c in range(n_chunks):
             lo, hi = bounds[c], bounds[c + 1]
+            n = hi - lo
             buf = bufs[c % len(bufs)]
             with torch.cuda.stream(s_in):
                 if c >= len(bufs):
                     s_in.wait_event(ev_done[c - len(bufs)])           # the kernels that read this buffer set are done
-                for d_, h_ in zip(buf, (q, k, v, do)):
-                    d_[: hi - lo].copy_(h_[lo:hi], non_blocking=True)
-                ev_in = torch.cuda.Event()
-                ev_in.record(s_in)
-            main.wait_event(ev_in)
-            leaves = [t[: hi - lo].detach().requires_grad_() for t in buf[:3]]
-            o = dm_attn_func(*leaves, softmax_scale=softmax_scale, causal=causal, mode=mode)
-            o.backward(buf[3][: hi - lo])
-            results = (o.detach(), leaves[0].grad, leaves[1].grad, leaves[2].grad)
+                for d_, h_ in zip(buf[:3], (q, k, v)):
+                    d_[:n].copy_(h_[lo:hi], non_blocking=True)
+                ev_qkv = torch.cuda.Event()
+                ev_qkv.record(s_in)
+                buf[3][:n].copy_(do[lo:hi], non_blocking=True)
+                ev_do = torch.cuda.Event()
+                ev_do.record(s_in)
+            # forward as soon as q, k, v are on the device
+            main.wait_event(ev_qkv)
+            qh, kh, vh, doh = (t[:n].transpose(1, 2) for t in buf)
+            q8, qs, k8, ks, v8, vs, _ = ops.quant_qkv(qh, kh, vh)
+            o, lse = ops.fwd_fp8(q8, k8, v8, qs, ks, vs, causal)
+            ev_fwd = torch.cuda.Event()
+            ev_fwd.record(main)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(ev_fwd)
+                o.record_stream(s_out)
+                out[0][lo:hi].copy_(o, non_blocking=True)
+            # backward once dO has arrived; O goes out meanwhile
+            main.wait_event(ev_do)
+            if mode == "matched":
+                do8, dos, _ = ops.quant_do(doh, None)
+                delta = ops.delta_fp8(q8, k8, v8, do8, qs, ks, vs, dos, lse, causal)
+            else:
+                do8, dos, delta = ops.quant_do(doh, o.permute(0, 2, 1, 3))
+            grads = ops.bwd_fp8(q8, k8, v8, do8, qs, ks, vs, dos, lse, delta, causal)
             done = torch.cuda.Event()
             done.record(main)
             ev_done.append(done)
             with torch.cuda.stream(s_out):
                 s_out.wait_event(done)
-                for h_, d_ in zip(out, results):
+                for h_, d_ in zip(out[1:], grads):
                     d_.record_stream(s_out)
                     h_[lo:hi].copy_(d_, non_blocking=True)
                 last_out = torch.cuda.Event()
