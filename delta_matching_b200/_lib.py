@@ -42,6 +42,7 @@ SIGNATURES = {
                        _P, _L, _L, _L, _P, _L, _L, _L, _P, _L, _L, _L, _P, _L, _I, _P, _P]),
     "dm_dbg_mma_tile": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P, _P]),
     "dm_dbg_mma_cycles": (_I, [_P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P, _P]),
+    "dm_copy_2d_async": (_I, [_P, _L, _P, _L, _L, _L, _I, _P]),
     "dm_kmean_static": (_I, [_P, _L, _L, _L, _I, _I, _I, _I, _P, _P, ctypes.c_char_p, _I]),
 }
 

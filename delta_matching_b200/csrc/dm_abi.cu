@@ -374,4 +374,17 @@ int dm_dbg_mma_cycles(const void* a, const void* b, int a_tmem, int a_mn, int b_
   return e == cudaSuccess ? 0 : cuda_fail(e, "probe launch");
 }
 
+int dm_copy_2d_async(void* dst, int64_t dpitch, const void* src, int64_t spitch, int64_t width, int64_t height,
+                     int to_device, void* stream) {
+  if (dst == nullptr || src == nullptr) return fail(DM_ERR_ARG, "delta_matching: dm_copy_2d_async: NULL pointer");
+  if (width < 0 || height < 0 || dpitch < width || spitch < width)
+    return fail(DM_ERR_ARG, "delta_matching: dm_copy_2d_async: pitches must be at least the row width");
+  if (width == 0 || height == 0) return 0;
+  cudaError_t e = cudaMemcpy2DAsync(dst, static_cast<size_t>(dpitch), src, static_cast<size_t>(spitch),
+                                    static_cast<size_t>(width), static_cast<size_t>(height),
+                                    to_device ? cudaMemcpyHostToDevice : cudaMemcpyDeviceToHost,
+                                    static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? 0 : cuda_fail(e, "strided copy");
+}
+
 }  // extern "C"

@@ -1,6 +1,6 @@
 """A training step of the attention fed from host memory: forward + backward with the copies pipelined.
 
-`attn_step_host` takes pinned CPU tensors, splits the batch into chunks (the (batch, head) problems are independent, so
+`attn_step_host` takes pinned CPU tensors, splits them into (batch, kv-head group) chunks (these problems are independent, so
 the results are bit-identical to one un-chunked call) and runs three streams: host->device copies of chunk c + 1,
 kernels of chunk c and device->host copies of chunk c - 1 overlap, which hides the compute and one direction of the
 PCIe traffic behind the other.  The device work is the op sequence of `dm_attn_func` and its backward
@@ -8,7 +8,11 @@ PCIe traffic behind the other.  The device work is the op sequence of `dm_attn_f
 """
 from __future__ import annotations
 
+import ctypes
+
 import torch
+
+from . import _lib
 
 _STREAMS = {}
 
@@ -38,8 +42,9 @@ def attn_step_host(q, k, v, do, *, causal=True, mode="matched", softmax_scale=No
 
     q, do: (B, N, H, D); k, v: (B, N, Hk, D); bf16, contiguous, pinned.  Returns (o, dq, dk, dv) as pinned CPU tensors
     (or fills `out`, a tuple of four such tensors).  The copies are asynchronous: the results are complete once the
-    current CUDA stream of `device` has been synchronised.  `chunks` (default: the batch size) is how many slices of
-    the batch are pipelined; argument errors are those of `dm_attn_func`.
+    current CUDA stream of `device` has been synchronised.  `chunks` is how many slices are pipelined: up to the batch
+    size they are batch ranges, beyond it (batch size times a divisor of nheads_k) ranges of kv-head groups of one batch,
+    moved with strided copies; the default aims at eight.  Argument errors are those of `dm_attn_func`.
 
     Per chunk: q, k, v are copied in and the forward starts while dO is still on its way; O is copied out while the
     backward runs; dQ, dK, dV follow.  The kernels are the ones `dm_attn_func` and its backward launch, in the same
@@ -53,10 +58,22 @@ def attn_step_host(q, k, v, do, *, causal=True, mode="matched", softmax_scale=No
     if k.shape != v.shape or k.shape[0] != q.shape[0]:
         raise ValueError("delta_matching: k and v must have equal shapes and the batch size of q")
     dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
-    B = q.shape[0]
-    n_chunks = B if chunks is None else int(chunks)
-    if n_chunks < 1 or n_chunks > B:
-        raise ValueError("delta_matching: chunks must be between 1 and the batch size")
+    B, N, H, D = q.shape
+    Hk = k.shape[2]
+    if Hk == 0 or H % Hk:
+        raise ValueError(f"delta_matching: nheads ({H}) must be a positive multiple of nheads_k ({Hk})")
+    rep = H // Hk
+    if chunks is None:
+        # about eight slices keep the pipeline's fill and drain short: whole batches if there are enough, else kv-group ranges
+        split = 1
+        while B * split < 8 and split * 2 <= Hk and Hk % (split * 2) == 0:
+            split *= 2
+        n_chunks = B * split if split > 1 else B
+    else:
+        n_chunks = int(chunks)
+    if n_chunks < 1 or n_chunks > B * Hk or (n_chunks > B and (n_chunks % B or Hk % (n_chunks // B))):
+        raise ValueError("delta_matching: chunks must be between 1 and the batch size, or the batch size times a divisor "
+                         "of nheads_k")
     if out is None:
         out = tuple(torch.empty(t.shape, dtype=torch.bfloat16).pin_memory() for t in (q, q, k, v))
     else:
@@ -64,47 +81,70 @@ def attn_step_host(q, k, v, do, *, causal=True, mode="matched", softmax_scale=No
             _check_host(name, t)
             if t.shape != like.shape:
                 raise ValueError(f"delta_matching: out tensor {name} has the wrong shape")
-    bounds = [(B * c) // n_chunks for c in range(n_chunks + 1)]
-    per = max(bounds[c + 1] - bounds[c] for c in range(n_chunks))
+    # a chunk is (batch range, kv-group range): whole batches, or a range of kv-head groups of one batch
+    if n_chunks <= B:
+        units = [((B * c) // n_chunks, (B * (c + 1)) // n_chunks, 0, Hk) for c in range(n_chunks)]
+    else:
+        gs = Hk // (n_chunks // B)
+        units = [(b, b + 1, g0, g0 + gs) for b in range(B) for g0 in range(0, Hk, gs)]
+    nb = max(u[1] - u[0] for u in units)
+    ng = max(u[3] - u[2] for u in units)
+    L = _lib.lib()
+
+    def copy(dev_t, host_t, b0, b1, h0, h1, to_device, stream):
+        """host_t[b0:b1, :, h0:h1, :] <-> the leading (b1 - b0) batches of the dense device tensor dev_t."""
+        heads, esz = host_t.shape[2], 2 * D
+        if h0 == 0 and h1 == heads:
+            rows, width, hpitch = (b1 - b0) * N, heads * esz, heads * esz
+        else:
+            rows, width, hpitch = N, (h1 - h0) * esz, heads * esz
+        hptr = host_t.data_ptr() + (b0 * N * heads + h0) * esz
+        if to_device:
+            rc = L.dm_copy_2d_async(ctypes.c_void_p(dev_t.data_ptr()), width, ctypes.c_void_p(hptr), hpitch, width, rows, 1,
+                                    ctypes.c_void_p(stream.cuda_stream))
+        else:
+            rc = L.dm_copy_2d_async(ctypes.c_void_p(hptr), hpitch, ctypes.c_void_p(dev_t.data_ptr()), width, width, rows, 0,
+                                    ctypes.c_void_p(stream.cuda_stream))
+        _lib.check(rc)
 
     with torch.cuda.device(dev), torch.no_grad():
         main = torch.cuda.current_stream(dev)
         s_in, s_out = _side_streams(dev)
-        # two sets of device input buffers, allocated on the main stream
-        bufs = [[torch.empty((per,) + tuple(t.shape[1:]), dtype=torch.bfloat16, device=dev) for t in (q, k, v, do)]
-                for _ in range(min(2, n_chunks))]
-        _check_inputs(*(t[:1].transpose(1, 2) for t in bufs[0][:3]), causal, softmax_scale, mode)
+        # two sets of device input buffers, allocated on the main stream; a chunk uses a dense leading part of each
+        sizes = (nb * N * ng * rep * D, nb * N * ng * D, nb * N * ng * D, nb * N * ng * rep * D)
+        bufs = [[torch.empty(n, dtype=torch.bfloat16, device=dev) for n in sizes] for _ in range(min(2, len(units)))]
+        probe = torch.empty(1, dtype=torch.bfloat16, device=dev)       # shape-only views for the input contract
+        _check_inputs(*(probe.expand(1, h, N, D) for h in (H, Hk, Hk)), causal, softmax_scale, mode)
         start = torch.cuda.Event()
         start.record(main)
         s_in.wait_event(start)
         s_out.wait_event(start)
         ev_done = []
         last_out = None
-        for c in range(n_chunks):
-            lo, hi = bounds[c], bounds[c + 1]
-            n = hi - lo
+        for c, (b0, b1, g0, g1) in enumerate(units):
+            n, hq, hg = b1 - b0, (g1 - g0) * rep, g1 - g0
             buf = bufs[c % len(bufs)]
-            with torch.cuda.stream(s_in):
-                if c >= len(bufs):
-                    s_in.wait_event(ev_done[c - len(bufs)])           # the kernels that read this buffer set are done
-                for d_, h_ in zip(buf[:3], (q, k, v)):
-                    d_[:n].copy_(h_[lo:hi], non_blocking=True)
-                ev_qkv = torch.cuda.Event()
-                ev_qkv.record(s_in)
-                buf[3][:n].copy_(do[lo:hi], non_blocking=True)
-                ev_do = torch.cuda.Event()
-                ev_do.record(s_in)
+            dq_, dk_, dv_, ddo_ = (t[: n * N * h * D].view(n, N, h, D) for t, h in zip(buf, (hq, hg, hg, hq)))
+            if c >= len(bufs):
+                s_in.wait_event(ev_done[c - len(bufs)])               # the kernels that read this buffer set are done
+            copy(dq_, q, b0, b1, g0 * rep, g1 * rep, True, s_in)
+            copy(dk_, k, b0, b1, g0, g1, True, s_in)
+            copy(dv_, v, b0, b1, g0, g1, True, s_in)
+            ev_qkv = torch.cuda.Event()
+            ev_qkv.record(s_in)
+            copy(ddo_, do, b0, b1, g0 * rep, g1 * rep, True, s_in)
+            ev_do = torch.cuda.Event()
+            ev_do.record(s_in)
             # forward as soon as q, k, v are on the device
             main.wait_event(ev_qkv)
-            qh, kh, vh, doh = (t[:n].transpose(1, 2) for t in buf)
+            qh, kh, vh, doh = (t.transpose(1, 2) for t in (dq_, dk_, dv_, ddo_))
             q8, qs, k8, ks, v8, vs, _ = ops.quant_qkv(qh, kh, vh)
             o, lse = ops.fwd_fp8(q8, k8, v8, qs, ks, vs, causal)
             ev_fwd = torch.cuda.Event()
             ev_fwd.record(main)
-            with torch.cuda.stream(s_out):
-                s_out.wait_event(ev_fwd)
-                o.record_stream(s_out)
-                out[0][lo:hi].copy_(o, non_blocking=True)
+            s_out.wait_event(ev_fwd)
+            o.record_stream(s_out)
+            copy(o, out[0], b0, b1, g0 * rep, g1 * rep, False, s_out)
             # backward once dO has arrived; O goes out meanwhile
             main.wait_event(ev_do)
             if mode == "matched":
@@ -112,17 +152,18 @@ def attn_step_host(q, k, v, do, *, causal=True, mode="matched", softmax_scale=No
                 delta = ops.delta_fp8(q8, k8, v8, do8, qs, ks, vs, dos, lse, causal)
             else:
                 do8, dos, delta = ops.quant_do(doh, o.permute(0, 2, 1, 3))
-            grads = ops.bwd_fp8(q8, k8, v8, do8, qs, ks, vs, dos, lse, delta, causal)
+            gq, gk, gv = ops.bwd_fp8(q8, k8, v8, do8, qs, ks, vs, dos, lse, delta, causal)
             done = torch.cuda.Event()
             done.record(main)
             ev_done.append(done)
-            with torch.cuda.stream(s_out):
-                s_out.wait_event(done)
-                for h_, d_ in zip(out[1:], grads):
-                    d_.record_stream(s_out)
-                    h_[lo:hi].copy_(d_, non_blocking=True)
-                last_out = torch.cuda.Event()
-                last_out.record(s_out)
+            s_out.wait_event(done)
+            for t in (gq, gk, gv):
+                t.record_stream(s_out)
+            copy(gq, out[1], b0, b1, g0 * rep, g1 * rep, False, s_out)
+            copy(gk, out[2], b0, b1, g0, g1, False, s_out)
+            copy(gv, out[3], b0, b1, g0, g1, False, s_out)
+            last_out = torch.cuda.Event()
+            last_out.record(s_out)
         main.wait_event(last_out)
         for buf in bufs:
             for t in buf:

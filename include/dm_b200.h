@@ -158,6 +158,13 @@ int dm_dbg_mma_cycles(const void* a, const void* b, int a_tmem, int a_mn, int b_
 int dm_kmean_static(const void* k, int64_t k_sb, int64_t k_sh, int64_t k_sn, int B, int N, int Hk, int D, float* mean,
                     void* stream, char* err, int err_len);
 
+/* Asynchronous strided copy between pinned host memory and device memory on a stream: `height` rows of `width` bytes,
+ * rows `spitch` / `dpitch` bytes apart; to_device != 0 copies host -> device.  A helper for callers that keep their
+ * tensors in host memory and feed (batch, head-range) slices of them to the entry points above (one cudaMemcpy2DAsync;
+ * the reference has no host-memory path).  Returns 0 or a negative code. */
+int dm_copy_2d_async(void* dst, int64_t dpitch, const void* src, int64_t spitch, int64_t width, int64_t height,
+                     int to_device, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

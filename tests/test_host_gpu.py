@@ -8,7 +8,7 @@ from .helpers import run_api
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("chunks", [None, 1, 2, 3])
+@pytest.mark.parametrize("chunks", [None, 1, 2, 3, 6])
 @pytest.mark.parametrize("mode,causal", [("matched", True), ("stale", False)])
 def test_host_step_is_bit_identical(chunks, mode, causal, oracle):
     from delta_matching_b200.host import attn_step_host
