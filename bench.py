@@ -330,7 +330,7 @@ def main():
         e2e = {"value": world * flops / (ms_e * 1e-3) / 1e12, "unit": "TFLOPS", "ms_per_step": ms_e,
                "h2d_bytes_per_step": sum(x.numel() * 2 for x in host_in),
                "d2h_bytes_per_step": sum(x.numel() * 2 for x in host_out),
-               "api": "delta_matching_b200.host.attn_step_host (pinned host tensors in and out, batch chunks pipelined)",
+               "api": "delta_matching_b200.host.attn_step_host (pinned host tensors in and out, (batch, kv-group range) chunks pipelined)",
                "ms_per_step_unpipelined": ms_serial}
     ops.check_status(dev)
 
