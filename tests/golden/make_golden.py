@@ -1,8 +1,9 @@
 """Generate the golden vectors of tests/golden/ by running the reference's own emulation.
 
-Run in a container where the reference checkout is mounted (default /root/reference, or pass its path):
+Run where a checkout of the reference (jet-ai-projects/delta-matching) is available and pass its path (or set
+DM_REFERENCE_ROOT):
 
-    python tests/golden/make_golden.py [/path/to/reference]
+    python tests/golden/make_golden.py /path/to/delta-matching
 
 It loads delta_matching/reference.py by file path (that file has no imports besides torch), runs `dm_reference` with the
 Blackwell presets on small seeded inputs, and writes one compressed .npz per case with the inputs (bf16 bit patterns),
@@ -40,7 +41,9 @@ def bits16(t):
 
 
 def main():
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("DM_REFERENCE_ROOT")
+    if not root:
+        sys.exit("usage: make_golden.py /path/to/delta-matching   (or set DM_REFERENCE_ROOT)")
     R = load_reference(root)
     torch.set_num_threads(max(1, os.cpu_count() or 1))
     for name, (B, N, H, Hk, D, causal, mode, seed, preset) in CASES.items():
