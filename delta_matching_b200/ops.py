@@ -227,6 +227,17 @@ def _workspace_cap_bytes() -> int:
 _MAX_WS_TILES = (1 << 24) - 1
 
 
+def plan_workspace_ranges(B: int, Hk: int, rep: int, n_t: int, group_bytes: int, cap: int):
+    """(batch start, batch end, kv-group start, kv-group end) ranges of one two-pass backward call each, such that the
+    dS workspace of a range (group_bytes per (batch, kv group)) stays within `cap` bytes and its tile count within the
+    limit of one call: whole batches when a batch fits, else kv-group ranges of one batch (at least one group)."""
+    groups_fit = max(1, min(Hk, cap // group_bytes, _MAX_WS_TILES // (rep * n_t * n_t)))
+    if groups_fit >= Hk:
+        bs = max(1, min(B, cap // (group_bytes * Hk), _MAX_WS_TILES // (rep * Hk * n_t * n_t)))
+        return [(b0, min(B, b0 + bs), 0, Hk) for b0 in range(0, B, bs)]
+    return [(b, b + 1, g0, min(Hk, g0 + groups_fit)) for b in range(B) for g0 in range(0, Hk, groups_fit)]
+
+
 def bwd_fp8(q8, k8, v8, do8, qs, ks, vs, dos, lse, delta, causal: bool, identity: bool = False, parts: int = 3,
             workspace=None):
     """-> (dq (B, N, H, D), dk (B, N, Hk, D), dv (B, N, Hk, D)) bf16; dk / dv are already reduced over the GQA group.
@@ -270,13 +281,7 @@ def bwd_fp8(q8, k8, v8, do8, qs, ks, vs, dos, lse, delta, causal: bool, identity
                 _require(workspace.dtype == torch.uint8 and workspace.is_contiguous() and workspace.device == dev,
                          "workspace must be a contiguous uint8 CUDA tensor on the inputs' device")
                 cap = workspace.numel()
-            # ranges of (batch, kv-head groups) whose workspace fits: whole batches if possible, else groups of one batch
-            groups_fit = max(1, min(Hk, cap // group_bytes, _MAX_WS_TILES // (rep * n_t * n_t)))
-            if groups_fit >= Hk:
-                bs = max(1, min(B, cap // (group_bytes * Hk), _MAX_WS_TILES // (H * n_t * n_t)))
-                ranges = [(b0, min(B, b0 + bs), 0, Hk) for b0 in range(0, B, bs)]
-            else:
-                ranges = [(b, b + 1, g0, min(Hk, g0 + groups_fit)) for b in range(B) for g0 in range(0, Hk, groups_fit)]
+            ranges = plan_workspace_ranges(B, Hk, rep, n_t, group_bytes, cap)
             need = max(bwd_workspace_bytes(b1 - b0, N, (g1 - g0) * rep, D) for b0, b1, g0, g1 in ranges)
             if workspace is None:
                 workspace = torch.empty(need, device=dev, dtype=torch.uint8)
