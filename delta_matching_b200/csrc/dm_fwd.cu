@@ -321,7 +321,11 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         DM_PROF_ADD(2, t2, t3);
         return true;
       };
+      DM_PROF_T(tia);
+      DM_PROF_ADD(6, ti0, tia);
       ok = p.causal ? tile(0, std::true_type{}) : tile(0, std::false_type{});
+      DM_PROF_T(tib);
+      DM_PROF_ADD(7, tia, tib);
       for (int it = 1; ok && it < n_it; ++it) ok = tile(it, std::false_type{});
       DM_PROF_T(ti1);
       if (ok) ok = wait_warp(bar_o, (gt - 1) & 1, abort_flag);
