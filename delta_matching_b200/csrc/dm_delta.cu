@@ -20,6 +20,16 @@
 
 namespace dm {
 
+#ifdef DM_PROFILE
+// Tuning build only (-DDM_PROFILE): cycle counters of compute warp 0 of CTA 0, read back with dm_prof_read_delta.
+__device__ long long g_delta_prof[16];
+#define DM_PROF_T(var) const long long var = clock64()
+#define DM_PROF_ADD(slot, a, b) prof[slot] += (b) - (a)
+#else
+#define DM_PROF_T(var)
+#define DM_PROF_ADD(slot, a, b)
+#endif
+
 template <int D>
 struct DeltaCfg {
   static constexpr int kSub = D / 128;
@@ -176,7 +186,12 @@ delta_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ C
     const int nblk = p.N / 32;
     uint32_t g = 0, n_done = 0;
     bool ok = true;
+#ifdef DM_PROFILE
+    long long prof[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    long long prof_tiles = 0;
+#endif
     for (int k = 0, item; (item = sched_item(k, blockIdx.x, gridDim.x)) < n_items; ++k, ++n_done) {
+      DM_PROF_T(ti0);
       int qt, bh;
       delta_item(item, n_qt, bh_count, qt, bh);
       const int bhk = (bh / p.H) * p.Hk + (bh % p.H) / (p.H / p.Hk);
@@ -200,7 +215,10 @@ delta_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ C
           vs1 = vs_base[(it + 1) * 4];
         }
         const bool diag = p.causal && (it == qt);
+        DM_PROF_T(t0);
         if (!(ok = wait_warp(bar_s + buf, (g >> 1) & 1, abort_flag))) break;
+        DM_PROF_T(t1);
+        DM_PROF_ADD(0, t0, t1);
         tc_fence_after();
         uint32_t s[32], dp[32];
         tmem_ld32(tmem + lane_base + buf * 256 + 32 * wg, s);
@@ -209,6 +227,8 @@ delta_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ C
         tc_fence_before();
         __syncwarp();
         if ((tid & 31) == 0) mbar_arrive(bar_c + buf);   // this warp's part of the buffer is in registers: hand it back
+        DM_PROF_T(t2);
+        DM_PROF_ADD(1, t1, t2);
         if (diag) {
 #pragma unroll
           for (int e = 0; e < 32; ++e)
@@ -230,7 +250,13 @@ delta_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ C
         const float db = (d0.x + d0.y) + (d1.x + d1.y);
         two_sum_acc(num_hi, num_lo, nb);
         two_sum_acc(den_hi, den_lo, db);
+        DM_PROF_T(t3);
+        DM_PROF_ADD(2, t2, t3);
+#ifdef DM_PROFILE
+        ++prof_tiles;
+#endif
       }
+      DM_PROF_T(ti1);
       // fold the groups' partial sums in fp64: groups 1-3 publish, group 0 adds in group order and stores.  Slots and
       // named barriers rotate over three items: a warp can run at most two tiles, hence two items, ahead of another.
       const int slot = n_done % 3;
@@ -251,13 +277,29 @@ delta_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ C
         }
         if (ok) p.delta[static_cast<size_t>(bh) * p.N + row] = static_cast<float>(n / dd);
       }
+      DM_PROF_T(ti2);
+      DM_PROF_ADD(3, ti1, ti2);
+      DM_PROF_ADD(4, ti0, ti2);
     }
+#ifdef DM_PROFILE
+    if (blockIdx.x == 0 && tid == 0) {
+      for (int i = 0; i < 8; ++i) g_delta_prof[i] = prof[i];
+      g_delta_prof[8] = prof_tiles;
+      g_delta_prof[9] = n_done;
+    }
+#endif
     if (!ok) raise_abort(abort_flag, p.status, kStatusTimeoutCompute);
   }
   tc_fence_before();
   __syncthreads();
   if (warp == 17) tmem_dealloc(tmem, C::kTmemCols);
 }
+
+#ifdef DM_PROFILE
+extern "C" int dm_prof_read_delta(long long* host16) {
+  return static_cast<int>(cudaMemcpyFromSymbol(host16, g_delta_prof, sizeof(long long) * 16));
+}
+#endif
 
 template <int D>
 static cudaError_t launch_delta_t(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
