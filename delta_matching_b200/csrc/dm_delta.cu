@@ -78,6 +78,9 @@ delta_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ C
   uint64_t* empty = bars + 6 + C::kStages;   // [kStages] the MMAs reading the stage are done
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 6 + 2 * C::kStages);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 7 + 2 * C::kStages);
+  uint64_t* bar_pub = bars + 20;   // [3] parts 1-3 have published their partial sums of the item (rotating slots)
+  uint64_t* bar_read = bars + 23;  // [3] part 0 has read the slot
+  static_assert(7 + 2 * C::kStages < 20, "barrier block layout");
 
   const int tid = threadIdx.x, warp = tid >> 5;
   const int n_qt = p.N / 128;
@@ -89,11 +92,15 @@ delta_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ C
     mbar_init(bar_qfree, 1);
     for (int s = 0; s < 2; ++s) {
       mbar_init(bar_s + s, 1);
-      mbar_init(bar_c + s, C::kGroups * 4);              // one arrival per compute warp
+      mbar_init(bar_c + s, C::kGroups * 2);              // one arrival per warp of the team that owns the tile
     }
     for (int s = 0; s < C::kStages; ++s) {
       mbar_init(full + s, 1);
       mbar_init(empty + s, 1);
+    }
+    for (int s = 0; s < 3; ++s) {
+      mbar_init(bar_pub + s, (C::kGroups - 1) * 4);
+      mbar_init(bar_read + s, 4);
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -180,9 +187,17 @@ delta_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ C
     }
   } else {
     // ------------------------------------------------------------------------------------------ compute groups
-    const int wg = warp >> 2;                          // key columns [32 wg, 32 wg + 32) of every tile: scale block wg
     const int r = tid & 127;                           // query row inside the tile = TMEM lane
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    // Two teams of eight warps alternate over the key tiles, so that one team's waits and TMEM loads run behind the other
+    // team's exponentials.  A team owns one S / dP buffer, i.e. the tiles of one parity of the CTA's running tile count
+    // (it waits on every phase of that buffer's barriers, so the phase parity is never ambiguous).  A thread takes 64
+    // key columns of a tile as two 32-column blocks.  Inside an item the team's tiles are those of one parity q of the
+    // tile index; the partial sums are filed under (q, column half), so that what is summed, and in which order, depends
+    // on the item only and not on which team did it.
+    const int team = warp >> 3;
+    const int half = (warp >> 2) & 1;
+    const int blk0 = 2 * half;                          // first of the thread's two key blocks (32 keys each)
     const int nblk = p.N / 32;
     uint32_t g = 0, n_done = 0;
     bool ok = true;
@@ -200,81 +215,100 @@ delta_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ C
       const float qs = p.qs[static_cast<size_t>(bh) * nblk + row / 32];
       const float dos = p.dos[static_cast<size_t>(bh) * nblk + row / 32];
       const float2 nl2 = splat2(-(p.lse[static_cast<size_t>(bh) * p.N + row] * kLog2e));
-      const float* ks_base = p.ks + static_cast<size_t>(bhk) * nblk + wg;
-      const float* vs_base = p.vs + static_cast<size_t>(bhk) * nblk + wg;
-      float ks1 = *ks_base, vs1 = *vs_base;
+      const float* ks_base = p.ks + static_cast<size_t>(bhk) * nblk + blk0;
+      const float* vs_base = p.vs + static_cast<size_t>(bhk) * nblk + blk0;
+      const int q = team ^ static_cast<int>(g & 1);    // parity of this team's tile indices inside the item
+      const int part = 2 * q + half;                   // index of this thread's partial sums in the item fold
+      float2 ks1 = make_float2(0.f, 0.f), vs1 = ks1;
+      if (q < n_it) {
+        ks1 = *reinterpret_cast<const float2*>(ks_base + q * 4);
+        vs1 = *reinterpret_cast<const float2*>(vs_base + q * 4);
+      }
       // running sums as unevaluated fp32 pairs (hi + lo, TwoSum): exact to ~2^-48 relative without the fp64 pipe
       float num_hi = 0.f, num_lo = 0.f, den_hi = 0.f, den_lo = 0.f;
-      for (int it = 0; ok && it < n_it; ++it, ++g) {
-        const uint32_t buf = g & 1;
-        const float2 c2 = splat2((ks1 * qs) * kLog2e);
-        // a = vs * dos is a power of two, so P * (dP_acc * a) == (P * dP_acc) * a exactly: a is applied once per block
-        const float a = vs1 * dos;
-        if (it + 1 < n_it) {                           // scales of the next key tile, in flight during this one
-          ks1 = ks_base[(it + 1) * 4];
-          vs1 = vs_base[(it + 1) * 4];
+      for (int it = q; ok && it < n_it; it += 2) {
+        const uint32_t gt = g + it;                    // the CTA's running tile count selects buffer and barrier phase
+        const uint32_t buf = gt & 1;
+        const float kss[2] = {ks1.x, ks1.y}, vss[2] = {vs1.x, vs1.y};
+        if (it + 2 < n_it) {                           // scales of the team's next key tile, in flight during this one
+          ks1 = *reinterpret_cast<const float2*>(ks_base + (it + 2) * 4);
+          vs1 = *reinterpret_cast<const float2*>(vs_base + (it + 2) * 4);
         }
         const bool diag = p.causal && (it == qt);
         DM_PROF_T(t0);
-        if (!(ok = wait_warp(bar_s + buf, (g >> 1) & 1, abort_flag))) break;
+        if (!(ok = wait_warp(bar_s + buf, (gt >> 1) & 1, abort_flag))) break;
         DM_PROF_T(t1);
         DM_PROF_ADD(0, t0, t1);
         tc_fence_after();
-        uint32_t s[32], dp[32];
-        tmem_ld32(tmem + lane_base + buf * 256 + 32 * wg, s);
-        tmem_ld32(tmem + lane_base + buf * 256 + 128 + 32 * wg, dp);
-        tmem_wait_ld();
-        tc_fence_before();
-        __syncwarp();
-        if ((tid & 31) == 0) mbar_arrive(bar_c + buf);   // this warp's part of the buffer is in registers: hand it back
-        DM_PROF_T(t2);
-        DM_PROF_ADD(1, t1, t2);
-        if (diag) {
 #pragma unroll
-          for (int e = 0; e < 32; ++e)
-            if (32 * wg + e > r) s[e] = 0xff800000u;     // -inf: key index above the query index
-        }
-        float2 n0 = make_float2(0.f, 0.f), n1 = n0, d0 = n0, d1 = n0;
+        for (int c = 0; c < 2; ++c) {
+          const int blk = blk0 + c;
+          const float2 c2 = splat2((kss[c] * qs) * kLog2e);
+          // a = vs * dos is a power of two, so P * (dP_acc * a) == (P * dP_acc) * a exactly: a is applied once per block
+          const float a = vss[c] * dos;
+          uint32_t s[32], dp[32];
+          tmem_ld32(tmem + lane_base + buf * 256 + 32 * blk, s);
+          tmem_ld32(tmem + lane_base + buf * 256 + 128 + 32 * blk, dp);
+          tmem_wait_ld();
+          if (c == 1) {                                // both blocks of this warp are in registers: hand the buffer back
+            tc_fence_before();
+            __syncwarp();
+            if ((tid & 31) == 0) mbar_arrive(bar_c + buf);
+          }
+          if (diag) {
 #pragma unroll
-        for (int e = 0; e < 16; e += 2) {
-          const float2 p0 = ex2_2(fma2(make_float2(__uint_as_float(s[2 * e]), __uint_as_float(s[2 * e + 1])), c2, nl2));
-          // three of the sixteen pairs take the polynomial: the MUFU pipe is the floor of this loop
-          const float2 x1 = fma2(make_float2(__uint_as_float(s[2 * e + 2]), __uint_as_float(s[2 * e + 3])), c2, nl2);
-          const float2 p1 = (e == 2 || e == 8 || e == 14) ? ex2_poly2(x1) : ex2_2(x1);
-          n0 = fma2(p0, make_float2(__uint_as_float(dp[2 * e]), __uint_as_float(dp[2 * e + 1])), n0);
-          n1 = fma2(p1, make_float2(__uint_as_float(dp[2 * e + 2]), __uint_as_float(dp[2 * e + 3])), n1);
-          d0 = add2(d0, p0);
-          d1 = add2(d1, p1);
+            for (int e = 0; e < 32; ++e)
+              if (32 * blk + e > r) s[e] = 0xff800000u;   // -inf: key index above the query index
+          }
+          float2 n0 = make_float2(0.f, 0.f), n1 = n0, d0 = n0, d1 = n0;
+#pragma unroll
+          for (int e = 0; e < 16; e += 2) {
+            const float2 p0 = ex2_2(fma2(make_float2(__uint_as_float(s[2 * e]), __uint_as_float(s[2 * e + 1])), c2, nl2));
+            // three of the sixteen pairs take the polynomial: the MUFU pipe is the floor of this loop
+            const float2 x1 = fma2(make_float2(__uint_as_float(s[2 * e + 2]), __uint_as_float(s[2 * e + 3])), c2, nl2);
+            const float2 p1 = (e == 2 || e == 8 || e == 14) ? ex2_poly2(x1) : ex2_2(x1);
+            n0 = fma2(p0, make_float2(__uint_as_float(dp[2 * e]), __uint_as_float(dp[2 * e + 1])), n0);
+            n1 = fma2(p1, make_float2(__uint_as_float(dp[2 * e + 2]), __uint_as_float(dp[2 * e + 3])), n1);
+            d0 = add2(d0, p0);
+            d1 = add2(d1, p1);
+          }
+          const float nb = ((n0.x + n0.y) + (n1.x + n1.y)) * a;
+          const float db = (d0.x + d0.y) + (d1.x + d1.y);
+          two_sum_acc(num_hi, num_lo, nb);
+          two_sum_acc(den_hi, den_lo, db);
         }
-        const float nb = ((n0.x + n0.y) + (n1.x + n1.y)) * a;
-        const float db = (d0.x + d0.y) + (d1.x + d1.y);
-        two_sum_acc(num_hi, num_lo, nb);
-        two_sum_acc(den_hi, den_lo, db);
         DM_PROF_T(t3);
-        DM_PROF_ADD(2, t2, t3);
+        DM_PROF_ADD(2, t1, t3);
 #ifdef DM_PROFILE
         ++prof_tiles;
 #endif
       }
+      g += static_cast<uint32_t>(n_it);
       DM_PROF_T(ti1);
-      // fold the groups' partial sums in fp64: groups 1-3 publish, group 0 adds in group order and stores.  Slots and
-      // named barriers rotate over three items: a warp can run at most two tiles, hence two items, ahead of another.
+      // Fold the four partial sums of a row in fp64: parts 1-3 publish, part 0 adds in part order and stores.  The slots
+      // (shared memory and two mbarriers each) rotate over three items: a publisher writes slot n % 3 only after part 0
+      // has read item n - 3 out of it, which also bounds how far a team can run ahead (it has no tile in a one-tile item).
       const int slot = n_done % 3;
+      const uint32_t slot_phase = (n_done / 3) & 1;
       double* red = sRed + slot * (3 * 128 * 2);
       const double num = static_cast<double>(num_hi) + static_cast<double>(num_lo);
       const double den = static_cast<double>(den_hi) + static_cast<double>(den_lo);
-      if (wg > 0) {
-        red[((wg - 1) * 128 + r) * 2] = num;
-        red[((wg - 1) * 128 + r) * 2 + 1] = den;
-        bar_arrive(1 + slot, C::kGroups * 128);
+      if (part > 0) {
+        if (ok && n_done >= 3) ok = wait_warp(bar_read + slot, slot_phase ^ 1, abort_flag);
+        red[((part - 1) * 128 + r) * 2] = num;
+        red[((part - 1) * 128 + r) * 2 + 1] = den;
+        __syncwarp();
+        if ((tid & 31) == 0) mbar_arrive(bar_pub + slot);
       } else {
-        bar_sync(1 + slot, C::kGroups * 128);
+        if (ok) ok = wait_warp(bar_pub + slot, slot_phase, abort_flag);
         double n = num, dd = den;
 #pragma unroll
         for (int gi = 0; gi < C::kGroups - 1; ++gi) {
           n += red[(gi * 128 + r) * 2];
           dd += red[(gi * 128 + r) * 2 + 1];
         }
+        __syncwarp();
+        if ((tid & 31) == 0) mbar_arrive(bar_read + slot);
         if (ok) p.delta[static_cast<size_t>(bh) * p.N + row] = static_cast<float>(n / dd);
       }
       DM_PROF_T(ti2);
