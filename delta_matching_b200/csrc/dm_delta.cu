@@ -226,6 +226,8 @@ delta_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ C
       }
       // running sums as unevaluated fp32 pairs (hi + lo, TwoSum): exact to ~2^-48 relative without the fp64 pipe
       float num_hi = 0.f, num_lo = 0.f, den_hi = 0.f, den_lo = 0.f;
+      DM_PROF_T(tia);
+      DM_PROF_ADD(5, ti0, tia);
       for (int it = q; ok && it < n_it; it += 2) {
         const uint32_t gt = g + it;                    // the CTA's running tile count selects buffer and barrier phase
         const uint32_t buf = gt & 1;
