@@ -45,7 +45,9 @@ struct FwdCfg {
   static constexpr int kSmemQ = 0;
   static constexpr int kSmemK = kTileBytes;
   static constexpr int kSmemV = kSmemK + kStages * kTileBytes;
-  static constexpr int kSmemBar = kSmemV + kStages * kTileBytes;
+  static constexpr int kSmemOut = kSmemV + kStages * kTileBytes;   // 4 warps x 32 rows x 80 bytes: O write-out staging
+  static constexpr int kOutRow = 80;                               // 64 bytes of a row + 16 of padding (bank spread)
+  static constexpr int kSmemBar = kSmemOut + 4 * 32 * kOutRow;
   static constexpr int kSmemBytes = kSmemBar + 256 + 1024;   // + slack for the 1024-byte alignment of the tile base
 };
 
@@ -334,8 +336,13 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       DM_PROF_ADD(3, ti1, ti2);
       tc_fence_after();
       const float inv_l = 1.0f / l;
-      __nv_bfloat16* orow = p.o + static_cast<int64_t>(b) * p.o_sb + static_cast<int64_t>(row) * p.o_sn +
-                            static_cast<int64_t>(h) * p.o_sh;
+      // A thread holds one row of O; written row by row, a warp's store would touch 32 rows with 16 bytes each.  Each
+      // 32-column chunk (64 bytes per row) goes through a per-warp staging area instead, from which four lanes write
+      // the 64 contiguous bytes of a row: a store instruction covers 8 rows completely.
+      const int lane = tid & 31;
+      const uint32_t stage_a = smem_u32(smem + C::kSmemOut) + warp * (32 * C::kOutRow);
+      const int out_row0 = qt * 128 + warp * 32;                    // first row of this warp
+      __nv_bfloat16* obase = p.o + static_cast<int64_t>(b) * p.o_sb + static_cast<int64_t>(h) * p.o_sh + 8 * (lane & 3);
 #pragma unroll 1
       for (int c = 0; c < D / 32; ++c) {
         uint32_t r[32];
@@ -347,9 +354,16 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
           __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(r[2 * e]) * inv_l, __uint_as_float(r[2 * e + 1]) * inv_l);
           w[e] = *reinterpret_cast<uint32_t*>(&v);
         }
-        uint4* dst = reinterpret_cast<uint4*>(orow + 32 * c);
+        __syncwarp();                                               // the previous chunk has been read out of the stage
 #pragma unroll
-        for (int e = 0; e < 4; ++e) dst[e] = make_uint4(w[4 * e], w[4 * e + 1], w[4 * e + 2], w[4 * e + 3]);
+        for (int e = 0; e < 4; ++e) sts_u4(stage_a + lane * C::kOutRow + 16 * e, w[4 * e], w[4 * e + 1], w[4 * e + 2], w[4 * e + 3]);
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int rr = 8 * i + (lane >> 2);                       // row of the warp this lane writes a quarter of
+          const float4 v = lds_f4(stage_a + rr * C::kOutRow + 16 * (lane & 3));
+          *reinterpret_cast<float4*>(obase + static_cast<int64_t>(out_row0 + rr) * p.o_sn + 32 * c) = v;
+        }
       }
       p.lse[static_cast<size_t>(bh) * p.N + row] = (m + log2f(l)) * kLn2;
       DM_PROF_T(ti3);
