@@ -32,6 +32,7 @@ SIGNATURES = {
                           _P, _P, _P, _P, _P, _P, _P, _P, _P]),
     "dm_quant_do": (_I, [_P, _L, _L, _L, _P, _L, _L, _L, _I, _I, _I, _I, _P, _P, _P, _P]),
     "dm_fwd": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _L, _L, _L, _P, _P, _P]),
+    "dm_dbg_fwd_unordered": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _L, _L, _L, _P, _P, _P]),
     "dm_delta": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _P, _P]),
     "dm_bwd": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I,
                     _P, _L, _L, _L, _P, _L, _L, _L, _P, _L, _L, _L, _P, _P, _P, _P]),
@@ -41,7 +42,8 @@ SIGNATURES = {
     "dm_bwd_ws": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I,
                        _P, _L, _L, _L, _P, _L, _L, _L, _P, _L, _L, _L, _P, _L, _I, _P, _P]),
     "dm_dbg_mma_tile": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P, _P]),
-    "dm_dbg_mma_cycles": (_I, [_P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P, _P]),
+    "dm_dbg_wait_expiry": (_I, [_P, _P, _P, ctypes.c_longlong, _P, _P]),
+    "dm_launch_count": (ctypes.c_longlong, []),
     "dm_copy_2d_async": (_I, [_P, _L, _P, _L, _L, _L, _I, _P]),
     "dm_kmean_static": (_I, [_P, _L, _L, _L, _I, _I, _I, _I, _P, _P, ctypes.c_char_p, _I]),
 }

@@ -12,6 +12,9 @@ from __future__ import annotations
 import torch
 
 from . import ops
+from . import torch_ops as _torch_ops  # noqa: F401  (registers torch.ops.delta_matching_b200.*)
+
+_OPS = torch.ops.delta_matching_b200
 
 
 def blocks(D: int):
@@ -62,18 +65,26 @@ def _check_inputs(q, k, v, causal, softmax_scale, mode):
     if softmax_scale is not None and abs(softmax_scale - D ** -0.5) > 1e-12:
         raise NotImplementedError(f"delta_matching: softmax_scale is fixed at head_dim ** -0.5 = {D ** -0.5!r} (it is "
                                   f"baked into the Q codes); got {softmax_scale!r}")
-    major, minor = torch.cuda.get_device_capability(q.device)
-    if major != 10:
+    if not _is_sm100(q.device.index if q.device.index is not None else torch.cuda.current_device()):
+        major, minor = torch.cuda.get_device_capability(q.device)
         raise ValueError(f"delta_matching: needs a Blackwell GPU (sm_100); {q.device} is sm{major}{minor}")
 
 
+@torch.compiler.assume_constant_result
+def _is_sm100(index: int) -> bool:
+    """A fact about the machine, not about the tensors: a tracing compiler may bake the answer into its graph."""
+    return torch.cuda.get_device_capability(index)[0] == 10
+
+
 class _DMAttn(torch.autograd.Function):
+    """Forward and backward as calls of the registered ops (delta_matching_b200/torch_ops.py), the way the reference's
+    autograd function calls torch.ops.delta_matching (delta_matching/attn.py:37-118): eager calls run the kernels
+    directly, and a tracing compiler records five opaque ops instead of breaking its graph here."""
 
     @staticmethod
     def forward(ctx, q, k, v, causal, delta_mode):
-        with torch.cuda.device(q.device):
-            q8, qs, k8, ks, v8, vs, _ = ops.quant_qkv(q, k, v)
-            o, lse = ops.fwd_fp8(q8, k8, v8, qs, ks, vs, causal)
+        q8, qs, k8, ks, v8, vs, _ = _OPS.quant_qkv(q, k, v)
+        o, lse = _OPS.fwd_fp8(q8, k8, v8, qs, ks, vs, causal)
         ctx.save_for_backward(q8, qs, k8, ks, v8, vs, o, lse)
         ctx.causal = causal
         ctx.delta_mode = delta_mode
@@ -83,26 +94,24 @@ class _DMAttn(torch.autograd.Function):
     @torch.autograd.function.once_differentiable
     def backward(ctx, dO):
         q8, qs, k8, ks, v8, vs, o, lse = ctx.saved_tensors
-        with torch.cuda.device(dO.device):
-            if dO.stride(-1) != 1:      # e.g. the expanded gradient of o.sum()
-                dO = dO.contiguous()
-            do_bhnd = dO.permute(0, 2, 1, 3)               # (B, N, H, D) -> (B, H, N, D) view, read in place
-            if ctx.delta_mode == "matched":
-                do8, dos, _ = ops.quant_do(do_bhnd, None)  # the matched mode never reads O
-                delta = ops.delta_fp8(q8, k8, v8, do8, qs, ks, vs, dos, lse, ctx.causal)
-            else:
-                do8, dos, delta = ops.quant_do(do_bhnd, o.permute(0, 2, 1, 3))
-            dq, dk, dv = ops.bwd_fp8(q8, k8, v8, do8, qs, ks, vs, dos, lse, delta, ctx.causal)
+        if dO.stride(-1) != 1:          # e.g. the expanded gradient of o.sum()
+            dO = dO.contiguous()
+        do_bhnd = dO.permute(0, 2, 1, 3)                   # (B, N, H, D) -> (B, H, N, D) view, read in place
+        if ctx.delta_mode == "matched":
+            do8, dos, _ = _OPS.quant_do(do_bhnd, do_bhnd, False)       # the matched mode never reads O
+            delta = _OPS.delta_fp8(q8, k8, v8, do8, qs, ks, vs, dos, lse, ctx.causal)
+        else:
+            do8, dos, delta = _OPS.quant_do(do_bhnd, o.permute(0, 2, 1, 3), True)
+        dq, dk, dv = _OPS.bwd_fp8(q8, k8, v8, do8, qs, ks, vs, dos, lse, delta, ctx.causal)
         return dq.permute(0, 2, 1, 3), dk.permute(0, 2, 1, 3), dv.permute(0, 2, 1, 3), None, None
 
 
-# The kernels are reached through ctypes, which a tracing compiler cannot look into: under torch.compile this call is a
-# graph break that runs eagerly (the reference reaches the same state with opaque torch.ops, tests/test_api.py:304-317).
-@torch.compiler.disable
 def dm_attn_func_bhnd(q, k, v, causal=True, softmax_scale=None, delta_mode="stale"):
     """Attention on (B, H, N, D) inputs: q (B, H, N, D), k / v (B, Hk, N, D) bf16 on CUDA (any strides; H % Hk == 0) ->
     O (B, N, H, D) bf16 contiguous.  delta_mode: "stale" (delta = rowsum(dO * O)) or "matched" (the Delta-Matching
-    backward; needs causal=True).  Input errors raise ValueError / TypeError / NotImplementedError."""
+    backward; needs causal=True).  Input errors raise ValueError / TypeError / NotImplementedError.  Works under
+    torch.compile without a graph break (the kernels are registered ops with fake implementations) and under CUDA-graph
+    capture after a warm-up call."""
     _check_inputs(q, k, v, causal, softmax_scale, delta_mode)
     return _DMAttn.apply(q, k, v, causal, delta_mode)
 

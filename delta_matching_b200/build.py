@@ -1,6 +1,6 @@
 """Build the CUDA library in-tree: nvcc for sm_100a only, one shared object `libdm_b200.so` next to this file.
 
-    python -m delta_matching_b200.build [--force] [--verbose] [--profile]
+    python -m delta_matching_b200.build [--force] [--verbose]
 
 The library exports the C ABI declared in include/dm_b200.h and links only against the CUDA runtime (the driver entry
 point for tensor-map encoding is resolved at run time), so it builds on a machine without a GPU.
@@ -47,12 +47,10 @@ def code_sha() -> str:
     return h.hexdigest()[:12]
 
 
-def build(force: bool = False, verbose: bool = False, profile: bool = False) -> str:
-    """Compile and link.  profile=True builds `libdm_b200_prof.so` with -DDM_PROFILE (section cycle counters inside the
-    forward and dK/dV kernels, read back with dm_prof_read_fwd / dm_prof_read_kv; load it with DM_SO): a tuning aid,
-    never the library the package loads by default."""
-    obj_dir = OBJ + ("_prof" if profile else "")
-    lib = LIB.replace(".so", "_prof.so") if profile else LIB
+def build(force: bool = False, verbose: bool = False) -> str:
+    """Compile and link (skipped when the library is newer than a stamp of the sources' hash)."""
+    obj_dir = OBJ
+    lib = LIB
     os.makedirs(obj_dir, exist_ok=True)
     stamp = os.path.join(obj_dir, "stamp.txt")
     sha = code_sha()
@@ -60,7 +58,7 @@ def build(force: bool = False, verbose: bool = False, profile: bool = False) -> 
         return lib
     srcs = list(SOURCES)
     nvcc = _nvcc()
-    flags = NVCC_FLAGS + (["-DDM_PROFILE"] if profile else [])
+    flags = NVCC_FLAGS
 
     def compile_one(src):
         obj = os.path.join(obj_dir, src[:-3] + ".o")
@@ -86,4 +84,4 @@ def build(force: bool = False, verbose: bool = False, profile: bool = False) -> 
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv, profile="--profile" in sys.argv))
+    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))

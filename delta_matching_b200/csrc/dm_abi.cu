@@ -2,6 +2,7 @@
 // no synchronisation.  Validation mirrors the op-level checks of csrc/delta_matching_api.cpp:73-98, 126-148 (device
 // memory, alignment, shape constraints, causal => equal sequence lengths by construction) and reports through
 // dm_last_error instead of TORCH_CHECK.
+#include <atomic>
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
@@ -9,6 +10,12 @@
 #include "../../include/dm_b200.h"
 #include "dm_kernels.h"
 #include "dm_probe.h"
+
+namespace dm {
+static std::atomic<long long> g_launches{0};
+void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+long long launch_count() { return g_launches.load(std::memory_order_relaxed); }
+}  // namespace dm
 
 namespace {
 
@@ -197,9 +204,10 @@ int dm_quant_do(const void* d_o, int64_t do_sb, int64_t do_sh, int64_t do_sn,
   return dm_quant_rows(d_o, do_sb, do_sh, do_sn, nullptr, 1.0f, o, o_sb, o_sh, o_sn, B, N, H, D, do8, dos, delta, stream);
 }
 
-int dm_fwd(const void* q8, const void* k8, const void* v8, const float* qs, const float* ks, const float* vs,
-           int B, int N, int H, int Hk, int D, int causal,
-           void* o, int64_t o_sb, int64_t o_sn, int64_t o_sh, float* lse, int* status, void* stream) {
+static int fwd_impl(const void* q8, const void* k8, const void* v8, const float* qs, const float* ks, const float* vs,
+                    int B, int N, int H, int Hk, int D, int causal,
+                    void* o, int64_t o_sb, int64_t o_sn, int64_t o_sh, float* lse, int* status, void* stream,
+                    int unordered) {
   DM_TRY(check_shape(B, N, H, Hk, D));
   DM_TRY(check_sm100());
   DM_TRY(check_device_ptr(q8, "q8")); DM_TRY(check_device_ptr(k8, "k8")); DM_TRY(check_device_ptr(v8, "v8"));
@@ -210,9 +218,22 @@ int dm_fwd(const void* q8, const void* k8, const void* v8, const float* qs, cons
   DM_TRY(make_code_map(&tq, q8, static_cast<uint64_t>(B) * H * N, D));
   DM_TRY(make_code_map(&tk, k8, static_cast<uint64_t>(B) * Hk * N, D));
   DM_TRY(make_code_map(&tv, v8, static_cast<uint64_t>(B) * Hk * N, D));
-  dm::FwdParams p{qs, ks, vs, static_cast<__nv_bfloat16*>(o), o_sb, o_sn, o_sh, lse, B, H, Hk, N, causal ? 1 : 0, status};
+  dm::FwdParams p{qs, ks, vs, static_cast<__nv_bfloat16*>(o), o_sb, o_sn, o_sh, lse, B, H, Hk, N, causal ? 1 : 0, status,
+                  unordered};
   cudaError_t e = dm::launch_fwd(D, tq, tk, tv, p, static_cast<cudaStream_t>(stream));
   return e == cudaSuccess ? 0 : cuda_fail(e, "forward launch");
+}
+
+int dm_fwd(const void* q8, const void* k8, const void* v8, const float* qs, const float* ks, const float* vs,
+           int B, int N, int H, int Hk, int D, int causal,
+           void* o, int64_t o_sb, int64_t o_sn, int64_t o_sh, float* lse, int* status, void* stream) {
+  return fwd_impl(q8, k8, v8, qs, ks, vs, B, N, H, Hk, D, causal, o, o_sb, o_sn, o_sh, lse, status, stream, 0);
+}
+
+int dm_dbg_fwd_unordered(const void* q8, const void* k8, const void* v8, const float* qs, const float* ks, const float* vs,
+                         int B, int N, int H, int Hk, int D, int causal,
+                         void* o, int64_t o_sb, int64_t o_sn, int64_t o_sh, float* lse, int* status, void* stream) {
+  return fwd_impl(q8, k8, v8, qs, ks, vs, B, N, H, Hk, D, causal, o, o_sb, o_sn, o_sh, lse, status, stream, 1);
 }
 
 int dm_delta(const void* q8, const void* k8, const void* v8, const void* do8,
@@ -352,27 +373,27 @@ int dm_dbg_mma_tile(const void* a, const void* b, const uint32_t* sfa, const uin
   CUtensorMap ta, tb;
   DM_TRY(make_code_map(&ta, a, 128, 128));
   DM_TRY(make_code_map(&tb, b, 128, 128));
-  dm::ProbeParams p{static_cast<const uint8_t*>(a), sfa, sfb, out, a_tmem, a_mn, b_mn, scaled, nk, status};
+  dm::ProbeParams p{static_cast<const uint8_t*>(a), sfa, sfb, out, a_tmem, a_mn, b_mn, scaled, nk, status, 0, 0};
   cudaError_t e = dm::launch_probe(ta, tb, p, static_cast<cudaStream_t>(stream));
   return e == cudaSuccess ? 0 : cuda_fail(e, "probe launch");
 }
 
-int dm_dbg_mma_cycles(const void* a, const void* b, int a_tmem, int a_mn, int b_mn, int scaled, int nk, int n_cols,
-                      int repeat, unsigned long long* cycles, int* status, void* stream) {
+int dm_dbg_wait_expiry(const void* a, const void* b, float* out, long long limit_ns, int* status, void* stream) {
   DM_TRY(check_sm100());
-  DM_TRY(check_device_ptr(a, "a")); DM_TRY(check_device_ptr(b, "b")); DM_TRY(check_device_ptr(cycles, "cycles"));
-  if (nk < 1 || nk > 4) return fail(DM_ERR_ARG, "delta_matching: nk must be in 1..4 (got %d)", nk);
-  if (n_cols != 64 && n_cols != 128) return fail(DM_ERR_ARG, "delta_matching: n_cols must be 64 or 128");
-  if (nk != 4) return fail(DM_ERR_ARG, "delta_matching: the timing probe issues groups of nk = 4 steps");
-  if (repeat < 1 || repeat > 4096) return fail(DM_ERR_ARG, "delta_matching: repeat must be in 1..4096");
-  if (a_tmem && a_mn) return fail(DM_ERR_ARG, "delta_matching: an A operand in TMEM has no major mode (a_mn must be 0)");
+  DM_TRY(check_device_ptr(a, "a")); DM_TRY(check_device_ptr(b, "b")); DM_TRY(check_device_ptr(out, "out"));
+  if (status == nullptr) return fail(DM_ERR_ARG, "delta_matching: the expiry probe needs a status word");
+  if (limit_ns < 1000 || limit_ns > 1000000000ll)
+    return fail(DM_ERR_ARG, "delta_matching: limit_ns must be between 1 microsecond and 1 second (got %lld)", limit_ns);
   CUtensorMap ta, tb;
   DM_TRY(make_code_map(&ta, a, 128, 128));
   DM_TRY(make_code_map(&tb, b, 128, 128));
-  dm::ProbeParams p{static_cast<const uint8_t*>(a), nullptr, nullptr, nullptr, a_tmem, a_mn, b_mn, scaled, nk, status};
-  cudaError_t e = dm::launch_mma_cycles(ta, tb, p, n_cols, repeat, cycles, static_cast<cudaStream_t>(stream));
+  dm::ProbeParams p{static_cast<const uint8_t*>(a), nullptr, nullptr, out, 0, 0, 0, 0, 4, status, 1,
+                    static_cast<uint64_t>(limit_ns)};
+  cudaError_t e = dm::launch_probe(ta, tb, p, static_cast<cudaStream_t>(stream));
   return e == cudaSuccess ? 0 : cuda_fail(e, "probe launch");
 }
+
+long long dm_launch_count(void) { return dm::launch_count(); }
 
 int dm_copy_2d_async(void* dst, int64_t dpitch, const void* src, int64_t spitch, int64_t width, int64_t height,
                      int to_device, void* stream) {

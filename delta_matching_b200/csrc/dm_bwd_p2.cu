@@ -265,6 +265,7 @@ cudaError_t launch_bwd_dq_p2(const CUtensorMap& tds, const CUtensorMap& tk, cons
   const int sms = (dev >= 0 && dev < 64) ? sm_count[dev] : 148;
   const int items = (p.N / 128) * p.B * p.H;
   bwd_dq_p2_kernel<<<items < sms ? items : sms, C::kThreads, C::kSmemBytes, stream>>>(tds, tk, p);
+  count_launch();
   return cudaGetLastError();
 }
 

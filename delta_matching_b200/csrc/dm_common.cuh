@@ -65,26 +65,29 @@ __device__ __forceinline__ uint64_t global_ns() {
   return t;
 }
 
-// Wait on an mbarrier phase for at most ~2 s of wall time, giving up early when another role of the CTA has already
-// raised the abort flag.  Returns false on give-up; the caller records a status code, raises the flag and leaves its loop.
+// Wait on an mbarrier phase for at most `limit_ns` of wall time (~2 s unless the caller passes its own limit), giving up
+// early when another role of the CTA has already raised the abort flag.  Returns false on give-up; the caller records a
+// status code, raises the flag and leaves its loop.
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
-__device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                              uint64_t limit_ns = kWaitLimitNs) {
   if (mbar_test_wait(bar, parity)) return true;      // the common case in a pipeline that runs ahead: already complete
   if (mbar_try_wait(bar, parity)) return true;
   // A waiting warp must not eat the issue slots of the warps it waits for: after a few immediate retries it sleeps
-  // between polls, and it looks at the abort flag and the clock only every 256 polls.
+  // between polls, and it looks at the abort flag and the clock only every 256 polls (every poll under a short limit).
 #pragma unroll 1
   for (int i = 0; i < 4; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
   }
   const uint64_t t0 = global_ns();
+  const uint32_t check_mask = (limit_ns < 100000000ull) ? 0u : 255u;
 #pragma unroll 1
   for (uint32_t spins = 1;; ++spins) {
     __nanosleep(40);
     if (mbar_try_wait(bar, parity)) return true;
-    if ((spins & 255u) == 0u) {
+    if ((spins & check_mask) == 0u) {
       if (*abort_flag != 0) return false;
-      if (global_ns() - t0 > kWaitLimitNs) return false;
+      if (global_ns() - t0 > limit_ns) return false;
     }
   }
 }
@@ -94,9 +97,15 @@ __device__ __forceinline__ bool wait_warp(uint64_t* bar, uint32_t parity, volati
   if (__all_sync(0xffffffffu, mbar_test_wait(bar, parity) ? 1 : 0) != 0) return true;   // ~30 cycles when complete
   return __all_sync(0xffffffffu, wait_or_abort(bar, parity, abort_flag) ? 1 : 0) != 0;
 }
+// The status word may live in pinned host memory that the GPU writes directly (the host then sees a give-up without a
+// copy): a plain store of the first code seen, no atomic; two roles racing here both hold a non-zero code.
 __device__ __forceinline__ void raise_abort(volatile int* abort_flag, int* status, int code) {
   *abort_flag = 1;
-  if (status != nullptr) atomicCAS(status, 0, code);
+  if (status != nullptr) {
+    volatile int* s = status;
+    if (*s == 0) *s = code;
+    __threadfence_system();
+  }
 }
 
 // Producer side of a named barrier: count towards the barrier without waiting (the consumers call bar_sync with the

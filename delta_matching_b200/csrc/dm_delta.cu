@@ -20,16 +20,6 @@
 
 namespace dm {
 
-#ifdef DM_PROFILE
-// Tuning build only (-DDM_PROFILE): cycle counters of compute warp 0 of CTA 0, read back with dm_prof_read_delta.
-__device__ long long g_delta_prof[16];
-#define DM_PROF_T(var) const long long var = clock64()
-#define DM_PROF_ADD(slot, a, b) prof[slot] += (b) - (a)
-#else
-#define DM_PROF_T(var)
-#define DM_PROF_ADD(slot, a, b)
-#endif
-
 template <int D>
 struct DeltaCfg {
   static constexpr int kSub = D / 128;
@@ -201,12 +191,7 @@ delta_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ C
     const int nblk = p.N / 32;
     uint32_t g = 0, n_done = 0;
     bool ok = true;
-#ifdef DM_PROFILE
-    long long prof[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    long long prof_tiles = 0;
-#endif
     for (int k = 0, item; (item = sched_item(k, blockIdx.x, gridDim.x)) < n_items; ++k, ++n_done) {
-      DM_PROF_T(ti0);
       int qt, bh;
       delta_item(item, n_qt, bh_count, qt, bh);
       const int bhk = (bh / p.H) * p.Hk + (bh % p.H) / (p.H / p.Hk);
@@ -226,8 +211,6 @@ delta_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ C
       }
       // running sums as unevaluated fp32 pairs (hi + lo, TwoSum): exact to ~2^-48 relative without the fp64 pipe
       float num_hi = 0.f, num_lo = 0.f, den_hi = 0.f, den_lo = 0.f;
-      DM_PROF_T(tia);
-      DM_PROF_ADD(5, ti0, tia);
       for (int it = q; ok && it < n_it; it += 2) {
         const uint32_t gt = g + it;                    // the CTA's running tile count selects buffer and barrier phase
         const uint32_t buf = gt & 1;
@@ -237,10 +220,7 @@ delta_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ C
           vs1 = *reinterpret_cast<const float2*>(vs_base + (it + 2) * 4);
         }
         const bool diag = p.causal && (it == qt);
-        DM_PROF_T(t0);
         if (!(ok = wait_warp(bar_s + buf, (gt >> 1) & 1, abort_flag))) break;
-        DM_PROF_T(t1);
-        DM_PROF_ADD(0, t0, t1);
         tc_fence_after();
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
@@ -265,10 +245,9 @@ delta_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ C
           float2 n0 = make_float2(0.f, 0.f), n1 = n0, d0 = n0, d1 = n0;
 #pragma unroll
           for (int e = 0; e < 16; e += 2) {
+            // every exponential is ex2.approx of the same fma as in the backward kernels: P is bitwise the backward's P
             const float2 p0 = ex2_2(fma2(make_float2(__uint_as_float(s[2 * e]), __uint_as_float(s[2 * e + 1])), c2, nl2));
-            // three of the sixteen pairs take the polynomial: the MUFU pipe is the floor of this loop
-            const float2 x1 = fma2(make_float2(__uint_as_float(s[2 * e + 2]), __uint_as_float(s[2 * e + 3])), c2, nl2);
-            const float2 p1 = (e == 2 || e == 8 || e == 14) ? ex2_poly2(x1) : ex2_2(x1);
+            const float2 p1 = ex2_2(fma2(make_float2(__uint_as_float(s[2 * e + 2]), __uint_as_float(s[2 * e + 3])), c2, nl2));
             n0 = fma2(p0, make_float2(__uint_as_float(dp[2 * e]), __uint_as_float(dp[2 * e + 1])), n0);
             n1 = fma2(p1, make_float2(__uint_as_float(dp[2 * e + 2]), __uint_as_float(dp[2 * e + 3])), n1);
             d0 = add2(d0, p0);
@@ -279,14 +258,8 @@ delta_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ C
           two_sum_acc(num_hi, num_lo, nb);
           two_sum_acc(den_hi, den_lo, db);
         }
-        DM_PROF_T(t3);
-        DM_PROF_ADD(2, t1, t3);
-#ifdef DM_PROFILE
-        ++prof_tiles;
-#endif
       }
       g += static_cast<uint32_t>(n_it);
-      DM_PROF_T(ti1);
       // Fold the four partial sums of a row in fp64: parts 1-3 publish, part 0 adds in part order and stores.  The slots
       // (shared memory and two mbarriers each) rotate over three items: a publisher writes slot n % 3 only after part 0
       // has read item n - 3 out of it, which also bounds how far a team can run ahead (it has no tile in a one-tile item).
@@ -313,29 +286,13 @@ delta_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ C
         if ((tid & 31) == 0) mbar_arrive(bar_read + slot);
         if (ok) p.delta[static_cast<size_t>(bh) * p.N + row] = static_cast<float>(n / dd);
       }
-      DM_PROF_T(ti2);
-      DM_PROF_ADD(3, ti1, ti2);
-      DM_PROF_ADD(4, ti0, ti2);
     }
-#ifdef DM_PROFILE
-    if (blockIdx.x == 0 && tid == 0) {
-      for (int i = 0; i < 8; ++i) g_delta_prof[i] = prof[i];
-      g_delta_prof[8] = prof_tiles;
-      g_delta_prof[9] = n_done;
-    }
-#endif
     if (!ok) raise_abort(abort_flag, p.status, kStatusTimeoutCompute);
   }
   tc_fence_before();
   __syncthreads();
   if (warp == 17) tmem_dealloc(tmem, C::kTmemCols);
 }
-
-#ifdef DM_PROFILE
-extern "C" int dm_prof_read_delta(long long* host16) {
-  return static_cast<int>(cudaMemcpyFromSymbol(host16, g_delta_prof, sizeof(long long) * 16));
-}
-#endif
 
 template <int D>
 static cudaError_t launch_delta_t(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
@@ -357,6 +314,7 @@ static cudaError_t launch_delta_t(const CUtensorMap& tq, const CUtensorMap& tk, 
   const int n_items = (p.N / 128) * p.B * p.H;
   const int ctas = (dev >= 0 && dev < 64) ? sm_count[dev] : 148;
   delta_kernel<D><<<n_items < ctas ? n_items : ctas, C::kThreads, C::kSmemBytes, stream>>>(tq, tk, tv, tdo, p);
+  count_launch();
   return cudaGetLastError();
 }
 

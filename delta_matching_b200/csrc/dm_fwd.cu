@@ -20,17 +20,6 @@
 
 namespace dm {
 
-#ifdef DM_PROFILE
-// Tuning build only (-DDM_PROFILE): cycle counters of softmax warp 0 of the first CTA, read back with cudaMemcpyFromSymbol.
-__device__ long long g_fwd1_prof[16];   // serial kernel
-__device__ long long g_fwd1_cta[4 * 1024];  // per CTA: start ns, end ns, tiles, SM id
-#define DM_PROF_T(var) const long long var = clock64()
-#define DM_PROF_ADD(slot, a, b) prof[slot] += (b) - (a)
-#else
-#define DM_PROF_T(var)
-#define DM_PROF_ADD(slot, a, b)
-#endif
-
 template <int D>
 struct FwdCfg {
   static constexpr int kSub = D / 128;                 // 128-byte-wide sub-tiles per operand row
@@ -55,7 +44,12 @@ struct FwdCfg {
 // of a list ordered by decreasing number of key tiles (item -> query tile n_qt - 1 - item / (B H), head item % (B H)).  The three roles keep
 // running tile / item counters for the barrier phases, so the K / V ring, the next Q tile and the next S run ahead into
 // the following item while the softmax warps still write out O of the current one.
-template <int D>
+// kOrdered: the MMA thread waits for the completion of the PV chain of tile i before it issues S of tile i + 1.  That S
+// chain overwrites the TMEM columns from which the PV chain reads its scale-factor words; the PTX ISA orders a later
+// MMA's accumulator writes behind an earlier MMA's operand reads, but does not say so for scale-factor reads (the
+// reference met the same question and answers it with a commit and a wait, delta_matching/sm100/dm_fwd_sm100.py:636-645).
+// kOrdered = false issues S(i + 1) straight behind PV(i) and relies on issue order alone.
+template <int D, bool kOrdered>
 __global__ void __launch_bounds__(192, (D == 128) ? 2 : 1)
 fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
            const __grid_constant__ CUtensorMap tm_v, const FwdParams p) {
@@ -153,6 +147,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
           const int st = gt % C::kStages;
           const uint32_t ph = (gt / C::kStages) & 1;
           if (!(ok = wait_or_abort(full_k + st, ph, abort_flag))) break;
+          // the previous PV chain (of this item or of the one before) has read its scale words out of the S columns
+          if (kOrdered && gt > 0 && !(ok = wait_or_abort(bar_o, (gt - 1) & 1, abort_flag))) break;
           tc_fence_after();
           // S = Q K^T: both operands K-major, k-step of 32 bytes inside the 128-byte swizzle row
           const uint32_t k_lo = k_lo0 + st * (C::kTileBytes >> 4), v_lo = v_lo0 + st * (C::kTileBytes >> 4);
@@ -180,8 +176,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
           }
           tc_commit(empty + st);
           tc_commit(bar_o);
-          // The next S chain overwrites the P codes and scale words this chain reads.  It is issued without waiting for
-          // this one: MMAs of one CTA execute in issue order, so its first write comes after this chain's last read.
+          // The next S chain overwrites the P codes and scale words this chain reads: see kOrdered above.
         }
       }
       if (!ok) raise_abort(abort_flag, p.status, kStatusTimeoutMma);
@@ -192,11 +187,6 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
     const int nblk = p.N / 32;
     bool ok = true;
     int gt = 0;
-#ifdef DM_PROFILE
-    long long prof[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    long long prof_tiles = 0, prof_items = 0;
-    const uint64_t prof_start_ns = global_ns();
-#endif
     // scalars of an item: head, query row, first key tile; the scales of item + 1 are requested one item ahead
     auto item_qs = [&](int item) -> const float* {
       const int qt = n_qt - 1 - item / BH, bh = item % BH;
@@ -215,7 +205,6 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       vs4 = *reinterpret_cast<const float4*>(item_kv(first_item, p.vs));
     }
     for (int k = 0, item; (item = sched_item(k, first_item, item_step)) < n_items; ++k) {
-      DM_PROF_T(ti0);
       const int qt = n_qt - 1 - item / BH, bh = item % BH;
       const int b = bh / p.H, h = bh % p.H;
       const int n_it = p.causal ? (qt + 1) : n_qt;
@@ -231,7 +220,6 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       // above the query index are masked; a compile-time variant so that the other tiles carry no select per element.
       auto tile = [&](int it, auto diag_tag) -> bool {
         constexpr bool kDiag = decltype(diag_tag)::value;
-        DM_PROF_T(t0);
         const float cb[4] = {qsl * ks4.x, qsl * ks4.y, qsl * ks4.z, qsl * ks4.w};
         const uint32_t sfb = pack4(scale_to_sb(vs4.x), scale_to_sb(vs4.y), scale_to_sb(vs4.z), scale_to_sb(vs4.w));
         // scales of the next key tile (of this item or of the next one): in flight while this tile is processed
@@ -245,8 +233,6 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
           vs4 = *reinterpret_cast<const float4*>(item_kv(item_n, p.vs));
         }
         if (!wait_warp(bar_s, gt & 1, abort_flag)) return false;
-        DM_PROF_T(t1);
-        DM_PROF_ADD(0, t0, t1);
         tc_fence_after();
         float bsum[4], kb[4], bmax[4];
         uint32_t r[2][32];
@@ -282,8 +268,6 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
           bsum[c] = sum0.x + sum0.y;
           tmem_st8(tmem + lane_base + C::kColS + 8 * c, codes);
         }
-        DM_PROF_T(t2);
-        DM_PROF_ADD(1, t1, t2);
         const float mcand = ceilf(fmaxf(fmaxf(bmax[0], bmax[1]), fmaxf(bmax[2], bmax[3])));
         float acc_scale = 1.0f;
         if (it == 0) {
@@ -319,21 +303,12 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         __syncwarp();
         if ((tid & 31) == 0) mbar_arrive(bar_p);
         ++gt;
-        DM_PROF_T(t3);
-        DM_PROF_ADD(2, t2, t3);
         return true;
       };
-      DM_PROF_T(tia);
-      DM_PROF_ADD(6, ti0, tia);
       ok = p.causal ? tile(0, std::true_type{}) : tile(0, std::false_type{});
-      DM_PROF_T(tib);
-      DM_PROF_ADD(7, tia, tib);
       for (int it = 1; ok && it < n_it; ++it) ok = tile(it, std::false_type{});
-      DM_PROF_T(ti1);
       if (ok) ok = wait_warp(bar_o, (gt - 1) & 1, abort_flag);
       if (!ok) break;
-      DM_PROF_T(ti2);
-      DM_PROF_ADD(3, ti1, ti2);
       tc_fence_after();
       const float inv_l = 1.0f / l;
       // A thread holds one row of O; written row by row, a warp's store would touch 32 rows with 16 bytes each.  Each
@@ -366,37 +341,15 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         }
       }
       p.lse[static_cast<size_t>(bh) * p.N + row] = (m + log2f(l)) * kLn2;
-      DM_PROF_T(ti3);
-      DM_PROF_ADD(4, ti2, ti3);
-      DM_PROF_ADD(5, ti0, ti3);
-#ifdef DM_PROFILE
-      prof_tiles += n_it;
-      ++prof_items;
-#endif
     }
     if (!ok) raise_abort(abort_flag, p.status, kStatusTimeoutCompute);
-#ifdef DM_PROFILE
-    if (blockIdx.x == 0 && tid == 0) {
-      for (int i = 0; i < 8; ++i) g_fwd1_prof[i] = prof[i];
-      g_fwd1_prof[8] = prof_tiles;
-      g_fwd1_prof[9] = prof_items;
-    }
-    if (tid == 0 && blockIdx.x < 1024) {
-      uint32_t smid;
-      asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
-      g_fwd1_cta[4 * blockIdx.x + 0] = static_cast<long long>(prof_start_ns);
-      g_fwd1_cta[4 * blockIdx.x + 1] = static_cast<long long>(global_ns());
-      g_fwd1_cta[4 * blockIdx.x + 2] = prof_tiles;
-      g_fwd1_cta[4 * blockIdx.x + 3] = smid;
-    }
-#endif
   }
   tc_fence_before();
   __syncthreads();
   if (warp == 5) tmem_dealloc(tmem, C::kTmemCols);
 }
 
-template <int D>
+template <int D, bool kOrdered>
 static cudaError_t launch_fwd_t(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FwdParams& p,
                                 cudaStream_t stream) {
   using C = FwdCfg<D>;
@@ -404,7 +357,7 @@ static cudaError_t launch_fwd_t(const CUtensorMap& tq, const CUtensorMap& tk, co
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(fwd_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+    cudaError_t e = cudaFuncSetAttribute(fwd_kernel<D, kOrdered>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
     if (e != cudaSuccess) return e;
     attr_set[dev] = true;
   }
@@ -416,24 +369,21 @@ static cudaError_t launch_fwd_t(const CUtensorMap& tq, const CUtensorMap& tk, co
   const int sms = (dev >= 0 && dev < 64) ? sm_count[dev] : 148;
   const int items = (p.N / 128) * p.B * p.H;
   const int ctas = sms * ((D == 128) ? 2 : 1);              // co-resident CTAs: 256 of the 512 TMEM columns each at D = 128
-  fwd_kernel<D><<<items < ctas ? items : ctas, 192, C::kSmemBytes, stream>>>(tq, tk, tv, p);
+  fwd_kernel<D, kOrdered><<<items < ctas ? items : ctas, 192, C::kSmemBytes, stream>>>(tq, tk, tv, p);
+  count_launch();
   return cudaGetLastError();
 }
 
-#ifdef DM_PROFILE
-extern "C" int dm_prof_read_fwd1_cta(long long* host4096) {
-  return static_cast<int>(cudaMemcpyFromSymbol(host4096, dm::g_fwd1_cta, sizeof(long long) * 4096));
-}
-extern "C" int dm_prof_read_fwd1(long long* host16) {
-  return static_cast<int>(cudaMemcpyFromSymbol(host16, dm::g_fwd1_prof, sizeof(long long) * 16));
-}
-#endif
 
 cudaError_t launch_fwd(int D, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FwdParams& p,
                        cudaStream_t stream) {
   // One kernel for both head dims: S (128 columns) plus O (head_dim columns) per CTA, two CTAs per SM at head_dim 128.
-  if (D != 128) return launch_fwd_t<256>(tq, tk, tv, p, stream);
-  return launch_fwd_t<128>(tq, tk, tv, p, stream);
+  if (p.unordered) {
+    if (D != 128) return launch_fwd_t<256, false>(tq, tk, tv, p, stream);
+    return launch_fwd_t<128, false>(tq, tk, tv, p, stream);
+  }
+  if (D != 128) return launch_fwd_t<256, true>(tq, tk, tv, p, stream);
+  return launch_fwd_t<128, true>(tq, tk, tv, p, stream);
 }
 
 }  // namespace dm

@@ -18,6 +18,7 @@ struct FwdParams {
   int B, H, Hk, N;
   int causal;
   int* status;
+  int unordered;               // S of the next tile issued without waiting for the PV chain (see fwd_kernel's kOrdered)
 };
 
 struct DeltaParams {
@@ -75,6 +76,10 @@ struct KMeanParams {
   float* mean;                 // (B, Hk, D)
   int B, Hk, N, D;
 };
+
+// Kernel launches made by the library in this process (every launcher counts its own).
+void count_launch(int n = 1);
+long long launch_count();
 
 cudaError_t launch_fwd(int D, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FwdParams& p,
                        cudaStream_t stream);

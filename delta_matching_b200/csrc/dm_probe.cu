@@ -1,7 +1,9 @@
 // One-tile tcgen05 building-block check: a 128 x 128 x (32 * nk) e4m3 product through exactly the operand paths the
 // attention kernels use (TMA 128-byte-swizzled tiles as K-major or MN-major shared-memory operands, A from TMEM, plain
 // kind::f8f6f4 and block-scaled kind::mxf8f6f4 with caller-supplied scale words).  Used by the unit tests to pin the
-// descriptor encodings and the TMEM scale-word placement against a host matmul.
+// descriptor encodings and the TMEM scale-word placement against a host matmul, and (skip_commit) to show what a bounded
+// wait does when it runs out: every thread gives up after wait_limit_ns, one of them records the status code, nobody
+// reads the accumulator, TMEM is freed and the kernel returns.
 #include "dm_common.cuh"
 #include "dm_kernels.h"
 #include "dm_probe.h"
@@ -83,13 +85,14 @@ probe_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
           else mma_f8_ss(tmem + kColD, da, db, id, acc);
         }
       }
-      tc_commit(bar_mma);
+      // skip_commit: the arrival everybody below waits for never comes, which makes their bounded wait run out
+      if (!p.skip_commit) tc_commit(bar_mma);
     } else {
       raise_abort(abort_flag, p.status, kStatusTimeoutProbe);
     }
   }
   __syncwarp();
-  ok = wait_or_abort(bar_mma, 0, abort_flag);
+  ok = wait_or_abort(bar_mma, 0, abort_flag, p.wait_limit_ns != 0 ? p.wait_limit_ns : kWaitLimitNs);
   if (ok) {
     tc_fence_after();
 #pragma unroll 1
@@ -109,154 +112,12 @@ probe_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
   if (warp == 0) tmem_dealloc(tmem, 256);
 }
 
-// Timing variant: `repeat` back-to-back groups of 4 MMAs (one 128-deep contraction) of width N into one accumulator,
-// everything about the MMA fixed at compile time so that the issue path is as short as in the attention kernels.
-// cycles[0] = first issue -> completion seen through the commit mbarrier, [1] = issue only, [2] = one
-// tcgen05.ld.32x32b.x32 + wait::ld in a compute warp, [3] = one MMA + commit -> completion (round trip).
-template <int N, bool SCALED, bool ATMEM, bool BMN, bool AMN = false>
-__global__ void __launch_bounds__(128, 1)
-mma_cycles_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b, int* status,
-                  int repeat, unsigned long long* cycles) {
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* sA = smem;
-  uint8_t* sB = smem + 16384;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 32768);
-  uint64_t* bar_load = bars + 0;
-  uint64_t* bar_mma = bars + 1;
-  uint64_t* bar_one = bars + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 4);
-  const int tid = threadIdx.x, warp = tid >> 5;
-  if (tid == 0) {
-    mbar_init(bar_load, 1);
-    mbar_init(bar_mma, 1);
-    mbar_init(bar_one, 1);
-    *abort_flag = 0;
-    mbar_fence_init();
-  }
-  if (warp == 0) {
-    tmem_alloc(tmem_slot, 512);
-    tmem_relinquish();
-    tc_fence_before();
-  }
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem = *tmem_slot;
-  const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
-  constexpr uint32_t kColD = 0, kColA = 256, kColSfa = 300, kColSfb = 304;
-  if (tid == 0) {
-    mbar_expect_tx(bar_load, 32768);
-    tma_load_2d(sA, &tm_a, bar_load, 0, 0);
-    tma_load_2d(sB, &tm_b, bar_load, 0, 0);
-  }
-  {
-    uint32_t r[32];
-#pragma unroll
-    for (int i = 0; i < 32; ++i) r[i] = 0x38383838u;          // four codes of 1.0
-    tmem_st32(tmem + lane_base + kColA, r);
-    tmem_st4(tmem + lane_base + kColSfa, 0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu);
-    tmem_st4(tmem + lane_base + kColSfb, 0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu);
-    tmem_wait_st();
-  }
-  tc_fence_before();
-  __syncthreads();
-  if (warp == 0) {
-    if (elect_one()) {
-      bool ok = wait_or_abort(bar_load, 0, abort_flag);
-      if (ok) {
-        tc_fence_after();
-        const uint32_t a_lo = desc_lo(smem_u32(sA)), b_lo = desc_lo(smem_u32(sB));
-        auto group = [&](bool first_acc) {
-#pragma unroll
-          for (int ks = 0; ks < 4; ++ks) {
-            const uint32_t db = b_lo + (BMN ? ks * 256 : ks * 2);
-            const bool acc = first_acc || ks > 0;
-            if (SCALED) {
-              if (ATMEM) mma_mxf8_ts(tmem + kColD, tmem + kColA + ks * 8, db, idesc_mxf8(128, N, false, BMN, ks, ks),
-                                     tmem + kColSfa, tmem + kColSfb, acc);
-              else mma_mxf8_ss(tmem + kColD, a_lo + (AMN ? ks * 256 : ks * 2), db, idesc_mxf8(128, N, AMN, BMN, ks, ks),
-                               tmem + kColSfa, tmem + kColSfb, acc);
-            } else {
-              if (ATMEM) mma_f8_ts(tmem + kColD, tmem + kColA + ks * 8, db, idesc_f8(128, N, false, BMN), acc);
-              else mma_f8_ss(tmem + kColD, a_lo + ks * 2, db, idesc_f8(128, N, false, BMN), acc);
-            }
-          }
-        };
-        long long t0 = clock64();
-        mma_f8_ss(tmem + kColD, a_lo, b_lo, idesc_f8(128, N, false, false), false);
-        tc_commit(bar_one);
-        ok = wait_or_abort(bar_one, 0, abort_flag);
-        long long t1 = clock64();
-        cycles[3] = static_cast<unsigned long long>(t1 - t0);
-        tc_fence_after();
-        t0 = clock64();
-#pragma unroll 1
-        for (int r = 0; r < repeat; ++r) group(r > 0);
-        tc_commit(bar_mma);
-        t1 = clock64();
-        ok = ok && wait_or_abort(bar_mma, 0, abort_flag);
-        const long long t2 = clock64();
-        cycles[0] = static_cast<unsigned long long>(t2 - t0);
-        cycles[1] = static_cast<unsigned long long>(t1 - t0);
-      }
-      if (!ok) raise_abort(abort_flag, status, kStatusTimeoutProbe);
-    }
-  }
-  __syncthreads();
-  tc_fence_after();
-  if (warp == 1) {
-    uint32_t r[32];
-    const long long t0 = clock64();
-    tmem_ld32(tmem + lane_base + kColD, r);
-    tmem_wait_ld();
-    const long long t1 = clock64();
-    uint32_t x = 0;
-#pragma unroll
-    for (int i = 0; i < 32; ++i) x ^= r[i];
-    if (tid == 32) {
-      cycles[2] = static_cast<unsigned long long>(t1 - t0);
-      cycles[4] = x;
-    }
-  }
-  tc_fence_before();
-  __syncthreads();
-  if (warp == 0) tmem_dealloc(tmem, 512);
-}
-
-template <int N, bool SCALED, bool ATMEM, bool BMN, bool AMN = false>
-static cudaError_t launch_cycles_t(const CUtensorMap& ta, const CUtensorMap& tb, int* status, int repeat,
-                                   unsigned long long* cycles, cudaStream_t stream) {
-  constexpr int kSmem = 32768 + 64 + 1024;
-  cudaError_t e = cudaFuncSetAttribute(mma_cycles_kernel<N, SCALED, ATMEM, BMN, AMN>,
-                                       cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
-  if (e != cudaSuccess) return e;
-  mma_cycles_kernel<N, SCALED, ATMEM, BMN, AMN><<<1, 128, kSmem, stream>>>(ta, tb, status, repeat, cycles);
-  return cudaGetLastError();
-}
-
-// Configurations the attention kernels use: plain K-major x K-major (S, dP), block-scaled with A in TMEM or in shared
-// memory and an MN-major B (PV, dV, dK, dQ), at widths 128 and 64.
-cudaError_t launch_mma_cycles(const CUtensorMap& ta, const CUtensorMap& tb, const ProbeParams& p, int n_cols, int repeat,
-                              unsigned long long* cycles, cudaStream_t stream) {
-  const int key = (n_cols == 128 ? 0 : 1) | (p.scaled ? 2 : 0) | (p.a_tmem ? 4 : 0) | (p.b_mn ? 8 : 0) | (p.a_mn ? 16 : 0);
-  switch (key) {
-    case 16 | 8 | 2: return launch_cycles_t<128, true, false, true, true>(ta, tb, p.status, repeat, cycles, stream);
-    case 0: return launch_cycles_t<128, false, false, false>(ta, tb, p.status, repeat, cycles, stream);
-    case 1: return launch_cycles_t<64, false, false, false>(ta, tb, p.status, repeat, cycles, stream);
-    case 8 | 4 | 2: return launch_cycles_t<128, true, true, true>(ta, tb, p.status, repeat, cycles, stream);
-    case 8 | 4 | 2 | 1: return launch_cycles_t<64, true, true, true>(ta, tb, p.status, repeat, cycles, stream);
-    case 8 | 2: return launch_cycles_t<128, true, false, true>(ta, tb, p.status, repeat, cycles, stream);
-    case 8 | 2 | 1: return launch_cycles_t<64, true, false, true>(ta, tb, p.status, repeat, cycles, stream);
-    default: return cudaErrorInvalidValue;
-  }
-}
-
 cudaError_t launch_probe(const CUtensorMap& ta, const CUtensorMap& tb, const ProbeParams& p, cudaStream_t stream) {
   constexpr int kSmem = 32768 + 64 + 1024;
   cudaError_t e = cudaFuncSetAttribute(probe_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
   if (e != cudaSuccess) return e;
   probe_kernel<<<1, 128, kSmem, stream>>>(ta, tb, p);
+  count_launch();
   return cudaGetLastError();
 }
 

@@ -16,10 +16,10 @@ struct ProbeParams {
   int scaled;                  // kind::mxf8f6f4.block_scale instead of kind::f8f6f4
   int nk;                      // 32-wide contraction steps (1..4); step k uses scale byte k
   int* status;
+  int skip_commit;             // the MMA role leaves out its commit: the waits of every thread run out (expiry check)
+  uint64_t wait_limit_ns;      // limit of those waits; 0 = the kernels' own limit
 };
 
-cudaError_t launch_mma_cycles(const CUtensorMap& ta, const CUtensorMap& tb, const ProbeParams& p, int n_cols, int repeat,
-                              unsigned long long* cycles, cudaStream_t stream);
 cudaError_t launch_probe(const CUtensorMap& ta, const CUtensorMap& tb, const ProbeParams& p, cudaStream_t stream);
 
 }  // namespace dm

@@ -23,6 +23,17 @@ __device__ __forceinline__ bool elect_one() {
   return pred != 0;
 }
 
+// Per-warpgroup register budget (setmaxnreg): every warp of a 128-thread group executes the same call.  A group that
+// needs few registers releases them, the others may then grow beyond what the launch allotted to every thread.
+template <int N>
+__device__ __forceinline__ void reg_dealloc() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <int N>
+__device__ __forceinline__ void reg_alloc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
+}
+
 // ------------------------------------------------------------------------------------------------ mbarrier
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
@@ -308,8 +319,9 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
   asm("max.f32 %0, %1, %2, %3;" : "=f"(m) : "f"(a), "f"(b), "f"(c));
   return m;
 }
-// 2^x on the FMA and integer pipes for a part of the exponentials (the MUFU pipe, 16 results per clock and SM, is the
-// floor of the attention kernels): round-to-nearest split x = n + f with f in [-0.5, 0.5] through the 1.5 * 2^23 trick,
+// 2^x on the FMA and integer pipes for a part of the forward's exponentials (the MUFU pipe, 16 results per clock and SM,
+// is the floor of the attention kernels; pass 0 and the backward kernels must produce one and the same P and therefore
+// all use ex2.approx): round-to-nearest split x = n + f with f in [-0.5, 0.5] through the 1.5 * 2^23 trick,
 // degree-5 polynomial for 2^f (2.4e-7 relative error in fp32, the accuracy of ex2.approx), n added to the exponent field.
 // Arguments below -120 are clamped (the result, < 1e-36, is zero for every use here); arguments must stay below 120.
 __device__ __forceinline__ float2 ex2_poly2(float2 x) {

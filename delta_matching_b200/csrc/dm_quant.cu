@@ -79,6 +79,7 @@ cudaError_t launch_kmean(const KMeanParams& p, cudaStream_t stream) {
   if (p.D == 128) kmean_partial_kernel<128><<<grid, 128, 0, stream>>>(p);
   else kmean_partial_kernel<256><<<grid, 128, 0, stream>>>(p);
   kmean_fold_kernel<<<p.B * p.Hk, 128, 0, stream>>>(p);
+  count_launch(2);
   return cudaGetLastError();
 }
 
@@ -163,6 +164,7 @@ cudaError_t launch_quant(const QuantParams& p, cudaStream_t stream) {
   dim3 grid(p.N / 32, p.B * p.H);
   if (p.D == 128) quant_kernel<128><<<grid, 128, 0, stream>>>(p);
   else quant_kernel<256><<<grid, 128, 0, stream>>>(p);
+  count_launch();
   return cudaGetLastError();
 }
 

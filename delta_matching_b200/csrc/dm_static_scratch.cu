@@ -30,6 +30,30 @@ int refuse(char* err, int err_len, int code, const char* msg) {
   return code;
 }
 
+// Device or managed memory that the current device owns, 16-byte aligned: the same demand dm_kmean makes of its
+// pointers.  cudaPointerGetAttributes allocates nothing.  Returns nullptr when the pointer passes, else the complaint.
+const char* bad_pointer(const void* ptr, int dev, const char* what, char* msg, size_t msg_len) {
+  cudaPointerAttributes a;
+  if (cudaPointerGetAttributes(&a, ptr) != cudaSuccess) {
+    cudaGetLastError();
+    snprintf(msg, msg_len, "delta_matching: %s must be CUDA memory", what);
+    return msg;
+  }
+  if (a.type != cudaMemoryTypeDevice && a.type != cudaMemoryTypeManaged) {
+    snprintf(msg, msg_len, "delta_matching: %s must be CUDA memory (got a host pointer)", what);
+    return msg;
+  }
+  if (a.type == cudaMemoryTypeDevice && a.device != dev) {
+    snprintf(msg, msg_len, "delta_matching: %s is on device %d but the current device is %d", what, a.device, dev);
+    return msg;
+  }
+  if (reinterpret_cast<uintptr_t>(ptr) & 15) {
+    snprintf(msg, msg_len, "delta_matching: %s must be 16-byte aligned", what);
+    return msg;
+  }
+  return nullptr;
+}
+
 }  // namespace
 
 extern "C" int dm_kmean_static(const void* k, int64_t k_sb, int64_t k_sh, int64_t k_sn, int B, int N, int Hk, int D,
@@ -48,7 +72,18 @@ extern "C" int dm_kmean_static(const void* k, int64_t k_sb, int64_t k_sh, int64_
   }
   int dev = -1;
   cudaError_t e = cudaGetDevice(&dev);
-  if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices) return refuse(err, err_len, -2, "delta_matching: cudaGetDevice failed");
+  if (e != cudaSuccess || dev < 0) return refuse(err, err_len, -2, "delta_matching: cudaGetDevice failed");
+  if (dev >= kMaxDevices) {
+    char msg[160];
+    snprintf(msg, sizeof(msg), "delta_matching: dm_kmean_static keeps its scratch address for devices 0..%d; the current "
+             "device is %d (use dm_kmean)", kMaxDevices - 1, dev);
+    return refuse(err, err_len, -1, msg);
+  }
+  {
+    char msg[200];
+    if (bad_pointer(k, dev, "k", msg, sizeof(msg)) != nullptr) return refuse(err, err_len, -1, msg);
+    if (bad_pointer(mean, dev, "mean", msg, sizeof(msg)) != nullptr) return refuse(err, err_len, -1, msg);
+  }
   float* scratch = nullptr;
   {
     std::lock_guard<std::mutex> lock(g_setup_mutex);

@@ -17,7 +17,7 @@ from . import _lib
 
 E4M3 = torch.float8_e4m3fn
 BLK = 32                                  # tokens per quantisation scale
-_STATUS = {}                              # device index -> int32 status word the kernels set on a bounded-wait timeout
+_STATUS = {}                              # device index -> int32 status word (pinned host memory the kernels write)
 _DEBUG = os.environ.get("DM_DEBUG", "0") not in ("", "0")
 
 STATUS_TEXT = {1: "TMA producer gave up waiting for a free stage", 2: "MMA issuer gave up waiting",
@@ -49,33 +49,58 @@ def _cuda(*ts):
     return dev
 
 
-def status_word(device) -> torch.Tensor:
-    """The per-device int32 word the kernels set when a bounded wait runs out (0 = no problem)."""
+def _dev_index(device) -> int:
     idx = torch.device(device).index
-    if idx is None:
-        idx = torch.cuda.current_device()
+    return torch.cuda.current_device() if idx is None else idx
+
+
+def status_word(device) -> torch.Tensor:
+    """The per-device int32 word the kernels set when a bounded wait runs out (0 = no problem).  It lives in pinned host
+    memory, which the GPU writes directly (pinned allocations are mapped into the device's address space under unified
+    addressing), so the host reads it without a copy and without a synchronisation."""
+    idx = _dev_index(device)
     w = _STATUS.get(idx)
     if w is None:
-        w = _STATUS[idx] = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", idx))
+        with torch.cuda.device(idx):
+            w = _STATUS[idx] = torch.zeros(1, dtype=torch.int32).pin_memory()
     return w
 
 
+def _raise_if_set(idx: int) -> None:
+    w = _STATUS.get(idx)
+    if w is None:
+        return
+    v = int(w[0])
+    if v != 0:
+        w[0] = 0
+        raise RuntimeError(f"delta_matching: a kernel on cuda:{idx} reported status {v} "
+                           f"({STATUS_TEXT.get(v, 'unknown')}); its outputs are invalid")
+
+
 def check_status(device=None) -> None:
-    """Synchronise and raise RuntimeError if a kernel on `device` reported a timed-out wait since the last check."""
-    devs = [torch.device(device).index] if device is not None else list(_STATUS)
+    """Synchronise `device` (every device used so far when None) and raise RuntimeError if one of its kernels reported a
+    timed-out wait since the last check."""
+    devs = [_dev_index(device)] if device is not None else list(_STATUS)
     for idx in devs:
-        if idx is None or idx not in _STATUS:
-            continue
-        v = int(_STATUS[idx].item())
-        if v != 0:
-            _STATUS[idx].zero_()
-            raise RuntimeError(f"delta_matching: a kernel on cuda:{idx} reported status {v} "
-                               f"({STATUS_TEXT.get(v, 'unknown')}); its outputs are invalid")
+        if idx in _STATUS:
+            torch.cuda.synchronize(idx)
+            _raise_if_set(idx)
+
+
+def _enter(device):
+    """At the entry of every op: a plain read of the pinned status word, no synchronisation.  A kernel that gave up
+    earlier on this device makes the next op raise instead of consuming its output."""
+    _raise_if_set(_dev_index(device))
 
 
 def _after(device):
     if _DEBUG and not torch.cuda.is_current_stream_capturing():
         check_status(device)
+
+
+def launch_count() -> int:
+    """Kernel launches the library has made in this process (counted by the library's launchers)."""
+    return int(_lib.lib().dm_launch_count())
 
 
 def _rows(x):
@@ -89,6 +114,7 @@ def _rows(x):
 def kmean(k: torch.Tensor) -> torch.Tensor:
     """k (B, Hk, N, D) bf16 -> (B, Hk, D) fp32 mean over tokens (fixed summation order)."""
     dev = _cuda(k)
+    _enter(dev)
     _require(k.dim() == 4 and k.dtype == torch.bfloat16, "k must be a 4-D bfloat16 tensor")
     k = _rows(k)
     B, Hk, N, D = k.shape
@@ -104,6 +130,7 @@ def quant_rows(x: torch.Tensor, prescale: float = 1.0, mean: torch.Tensor | None
     """x (B, H, N, D) bf16 -> (codes (B, H, N, D) e4m3, scales (B, H, N // 32) fp32[, delta (B, H, N) fp32 if o given]).
     y = (x - mean[b, h]) * prescale is quantised; delta = sum_d x * o on the raw values."""
     dev = _cuda(x, mean, o)
+    _enter(dev)
     _require(x.dim() == 4 and x.dtype == torch.bfloat16, "input must be a 4-D bfloat16 tensor")
     x = _rows(x)
     B, H, N, D = x.shape
@@ -130,6 +157,7 @@ def quant_qkv(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor):
     """q (B, H, N, D), k / v (B, Hk, N, D) bf16 -> (q8, qs, k8, ks, v8, vs, kmean).  q is scaled by D^-0.5, k is centred
     by its per-(batch, kv head) mean over tokens (returned as kmean (B, Hk, D) fp32)."""
     dev = _cuda(q, k, v)
+    _enter(dev)
     for t in (q, k, v):
         _require(t.dim() == 4 and t.dtype == torch.bfloat16, "q, k, v must be 4-D bfloat16 tensors")
     q, k, v = _rows(q), _rows(k), _rows(v)
@@ -172,9 +200,11 @@ def _check_codes(B, H, Hk, N, D, q8, k8, v8, qs, ks, vs, do8=None, dos=None):
         _require(tuple(t.shape) == (B, h, N // BLK) and t.is_contiguous(), f"{name} must be contiguous (B, H, N // 32)")
 
 
-def fwd_fp8(q8, k8, v8, qs, ks, vs, causal: bool):
-    """-> (O (B, N, H, D) bf16 contiguous, LSE (B, H, N) fp32 natural log).  Replaces the fwd_fp8 op."""
+def fwd_fp8(q8, k8, v8, qs, ks, vs, causal: bool, unordered: bool = False):
+    """-> (O (B, N, H, D) bf16 contiguous, LSE (B, H, N) fp32 natural log).  Replaces the fwd_fp8 op.  unordered=True is
+    the test hook dm_dbg_fwd_unordered (same results, one ordering wait per key tile fewer)."""
     dev = _cuda(q8, k8, v8, qs, ks, vs)
+    _enter(dev)
     _require(q8.dim() == 4 and k8.dim() == 4, "codes must be 4-D")
     B, H, N, D = q8.shape
     Hk = k8.shape[1]
@@ -183,8 +213,9 @@ def fwd_fp8(q8, k8, v8, qs, ks, vs, causal: bool):
     with torch.cuda.device(dev):
         o = torch.empty(B, N, H, D, device=dev, dtype=torch.bfloat16)
         lse = torch.empty(B, H, N, device=dev, dtype=torch.float32)
-        _lib.check(L.dm_fwd(_ptr(q8), _ptr(k8), _ptr(v8), _ptr(qs), _ptr(ks), _ptr(vs), B, N, H, Hk, D, int(bool(causal)),
-                            _ptr(o), o.stride(0), o.stride(1), o.stride(2), _ptr(lse), _ptr(status_word(dev)), _stream(q8)))
+        fn = L.dm_dbg_fwd_unordered if unordered else L.dm_fwd
+        _lib.check(fn(_ptr(q8), _ptr(k8), _ptr(v8), _ptr(qs), _ptr(ks), _ptr(vs), B, N, H, Hk, D, int(bool(causal)),
+                      _ptr(o), o.stride(0), o.stride(1), o.stride(2), _ptr(lse), _ptr(status_word(dev)), _stream(q8)))
         _after(dev)
     return o, lse
 
@@ -192,6 +223,7 @@ def fwd_fp8(q8, k8, v8, qs, ks, vs, causal: bool):
 def delta_fp8(q8, k8, v8, do8, qs, ks, vs, dos, lse, causal: bool):
     """-> matched delta (B, H, N) fp32 from pass 0 of the backward.  Replaces the delta_fp8 op."""
     dev = _cuda(q8, k8, v8, do8, qs, ks, vs, dos, lse)
+    _enter(dev)
     B, H, N, D = q8.shape
     Hk = k8.shape[1]
     _check_codes(B, H, Hk, N, D, q8, k8, v8, qs, ks, vs, do8, dos)
@@ -210,10 +242,11 @@ def bwd_workspace_bytes(B: int, N: int, H: int, D: int) -> int:
     return int(_lib.lib().dm_bwd_workspace_bytes(int(B), int(N), int(H), int(D)))
 
 
-def _workspace_cap_bytes() -> int:
+def _workspace_cap_bytes(device=None) -> int:
     """Bound of the dS workspace of one backward call: DM_BWD_WORKSPACE_MB (MiB; 0 selects the backward that recomputes
     instead of storing), else the reference's own knob DM_BWD_WS_LIMIT_GB (delta_matching/split.py:37-97 bounds the same
-    buffer by splitting the call per head group), else 16 GiB."""
+    buffer by splitting the call per head group), else 60 % of the device memory that is free or held idle by torch's
+    caching allocator (at least 4 GiB), so that on a 180 GB GPU many (batch, kv-group) units share one launch."""
     try:
         if "DM_BWD_WORKSPACE_MB" in os.environ:
             return int(os.environ["DM_BWD_WORKSPACE_MB"]) << 20
@@ -221,7 +254,11 @@ def _workspace_cap_bytes() -> int:
             return int(float(os.environ["DM_BWD_WS_LIMIT_GB"]) * (1 << 30))
     except ValueError:
         pass
-    return 16384 << 20
+    if device is None or torch.cuda.is_current_stream_capturing():
+        return 16384 << 20
+    free, _ = torch.cuda.mem_get_info(device)
+    idle = torch.cuda.memory_reserved(device) - torch.cuda.memory_allocated(device)
+    return max(4 << 30, int(0.6 * (free + idle)))
 
 
 _MAX_WS_TILES = (1 << 24) - 1
@@ -250,6 +287,7 @@ def bwd_fp8(q8, k8, v8, do8, qs, ks, vs, dos, lse, delta, causal: bool, identity
     `workspace` (uint8, at least bwd_workspace_bytes) is given; when it would exceed DM_BWD_WORKSPACE_MB the call is
     split over (batch, kv-head group) ranges, and when a single group exceeds it the recomputing kernel runs."""
     dev = _cuda(q8, k8, v8, do8, qs, ks, vs, dos, lse, delta)
+    _enter(dev)
     B, H, N, D = q8.shape
     Hk = k8.shape[1]
     _check_codes(B, H, Hk, N, D, q8, k8, v8, qs, ks, vs, do8, dos)
@@ -258,7 +296,7 @@ def bwd_fp8(q8, k8, v8, do8, qs, ks, vs, dos, lse, delta, causal: bool, identity
     L = _lib.lib()
     rep = H // Hk
     n_t = N // 128
-    cap = _workspace_cap_bytes()
+    cap = _workspace_cap_bytes(dev)
     group_bytes = bwd_workspace_bytes(1, N, rep, D)
     two_pass = (D == 128 and not identity and group_bytes > 0 and (workspace is not None or group_bytes <= cap)
                 and rep * n_t * n_t <= _MAX_WS_TILES)
@@ -309,9 +347,22 @@ def mma_tile(a, b, sfa=None, sfb=None, a_tmem=False, a_mn=False, b_mn=False, nk=
     """One 128 x 128 x (32 nk) tile product through the kernels' operand paths (see dm_dbg_mma_tile); a, b uint8 /
     e4m3 (128, 128); sfa / sfb int32 (128, 4) scale words select the block-scaled instruction."""
     dev = _cuda(a, b, sfa, sfb)
+    _enter(dev)
     L = _lib.lib()
     with torch.cuda.device(dev):
         out = torch.empty(128, 128, device=dev, dtype=torch.float32)
         _lib.check(L.dm_dbg_mma_tile(_ptr(a), _ptr(b), _ptr(sfa), _ptr(sfb), int(a_tmem), int(a_mn), int(b_mn),
                                      int(sfa is not None), int(nk), _ptr(out), _ptr(status_word(dev)), _stream(a)))
+    return out
+
+
+def wait_expiry_probe(a, b, limit_us: int = 100):
+    """Launch the one-tile kernel with the arrival its threads wait for left out and `limit_us` as the limit of that wait
+    (dm_dbg_wait_expiry): the kernel returns by itself and leaves status 4 in the device's status word.  -> the (unwritten)
+    output tensor.  Used by the tests to show the give-up path end to end."""
+    dev = _cuda(a, b)
+    L = _lib.lib()
+    with torch.cuda.device(dev):
+        out = torch.zeros(128, 128, device=dev, dtype=torch.float32)
+        _lib.check(L.dm_dbg_wait_expiry(_ptr(a), _ptr(b), _ptr(out), int(limit_us) * 1000, _ptr(status_word(dev)), _stream(a)))
     return out

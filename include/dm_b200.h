@@ -82,6 +82,15 @@ int dm_fwd(const void* q8, const void* k8, const void* v8, const float* qs, cons
            int B, int N, int H, int Hk, int D, int causal,
            void* o, int64_t o_sb, int64_t o_sn, int64_t o_sh, float* lse, int* status, void* stream);
 
+/* dm_fwd with the S chain of the next key tile issued straight behind the PV chain of the current one, without the
+ * commit-and-wait that dm_fwd puts between them (the next S overwrites the TMEM columns the PV chain reads its scale
+ * words from; the reference documents the hazard and orders the two, delta_matching/sm100/dm_fwd_sm100.py:636-645).
+ * Test hook: the unit tests demand bitwise equal O and LSE from both forms and the benchmark reports what the ordering
+ * costs.  Not a production entry point. */
+int dm_dbg_fwd_unordered(const void* q8, const void* k8, const void* v8, const float* qs, const float* ks, const float* vs,
+                         int B, int N, int H, int Hk, int D, int causal,
+                         void* o, int64_t o_sb, int64_t o_sn, int64_t o_sh, float* lse, int* status, void* stream);
+
 /* Matched delta (pass 0): delta_i = sum_j P_ij dP_ij / sum_j P_ij from the backward's own P / dP recompute.
  * Replaces the delta_fp8 op (csrc/delta_matching_api.cpp:470-609). */
 int dm_delta(const void* q8, const void* k8, const void* v8, const void* do8,
@@ -138,11 +147,14 @@ int dm_bwd_ws(const void* q8, const void* k8, const void* v8, const void* do8,
 int dm_dbg_mma_tile(const void* a, const void* b, const uint32_t* sfa, const uint32_t* sfb, int a_tmem, int a_mn,
                     int b_mn, int scaled, int nk, float* out, int* status, void* stream);
 
-/* Timing companion of dm_dbg_mma_tile (unit-test / tuning hook, no counterpart in the reference): `repeat` groups of nk
- * MMAs of width n_cols issued back to back into one accumulator by one CTA.  cycles (device, 5 x uint64): [0] first
- * issue -> completion, [1] issue only, [2] one 32-column TMEM load + wait, [3] one MMA + commit round trip. */
-int dm_dbg_mma_cycles(const void* a, const void* b, int a_tmem, int a_mn, int b_mn, int scaled, int nk, int n_cols,
-                      int repeat, unsigned long long* cycles, int* status, void* stream);
+/* The same one-tile kernel with the arrival its threads wait for left out, and with `limit_ns` as the limit of that
+ * wait: shows what every bounded wait of the library does when it runs out (the reference's kernels spin without a
+ * bound; this has no counterpart there).  The kernel returns by itself after about limit_ns, *status becomes
+ * DM_STATUS_TIMEOUT_PROBE (4), out is left unwritten, the context stays usable.  a, b as in dm_dbg_mma_tile. */
+int dm_dbg_wait_expiry(const void* a, const void* b, float* out, long long limit_ns, int* status, void* stream);
+
+/* Kernel launches this library has made in this process so far (all devices, all streams). */
+long long dm_launch_count(void);
 
 /* K mean without a workspace argument, for callers that cannot allocate device memory themselves (code inside a
  * no-allocation region of its host framework, or a plugin that owns no memory pool): same inputs, same kernels and

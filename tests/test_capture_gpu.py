@@ -1,6 +1,6 @@
 """torch.compile and CUDA-graph capture around the public API, as the reference tests them (tests/test_api.py:304-332):
-the compiled / replayed results equal the eager ones bit for bit.  The backward is captured too (the reference captures
-the forward only)."""
+the compiled / replayed results equal the eager ones bit for bit, and the compiler traces through the API without a
+graph break.  The backward is captured too (the reference captures the forward only)."""
 import pytest
 import torch
 
@@ -66,3 +66,20 @@ def test_torch_compile_matches_eager(oracle):
     ob.backward(go)
     torch.cuda.synchronize()
     assert torch.equal(oa, ob) and torch.equal(qa.grad, qb.grad) and torch.equal(ka.grad, kb.grad) and torch.equal(va.grad, vb.grad)
+
+
+def test_torch_compile_traces_without_a_graph_break(oracle):
+    """The API is made of registered ops with fake implementations (torch.ops.delta_matching_b200.*), so dynamo traces
+    through dm_attn_func instead of falling back to eager around it (reference: tests/test_api.py:304-317)."""
+    import torch._dynamo
+    from delta_matching_b200 import dm_attn_func
+    q, k, v, _ = _inputs(oracle, 44)
+
+    def f(q, k, v):
+        return dm_attn_func(q * 1.0, k, v, causal=True, mode="matched") + 0.0
+    torch._dynamo.reset()
+    ex = torch._dynamo.explain(f)(q.detach().requires_grad_(True), k, v)
+    assert ex.graph_break_count == 0, ex.break_reasons
+    assert ex.graph_count == 1
+    names = {str(n.target) for g in ex.graphs for n in g.graph.nodes}
+    assert any("autograd_function_apply" in n or "delta_matching_b200" in n for n in names), names

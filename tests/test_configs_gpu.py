@@ -10,30 +10,43 @@ pytestmark = pytest.mark.gpu
 NAMES = ("O", "dQ", "dK", "dV")
 
 
+# Distance of the kernel to the emulation per logit scale s, measured on B200 at the configuration's full size
+# (DM_TEST_RECORD) and gated at about three times the measurement.  At s = 1 the gates are the reference's own
+# (tests/test_sm100.py:61: 3e-4 for O, 5e-3 for the gradients).  From s = 3 on the logits reach hundreds to thousands of
+# log2 units, so one fp32 rounding of S * c moves P by up to 2^-24 * |x|: the distance grows with s for a kernel that
+# evaluates fma(S, c, bias) in one rounding while the emulation multiplies and subtracts in two.
+SWEEP_GATES = {1.0: dict(O=3e-4, g=5e-3), 3.0: dict(O=6e-4, g=6e-3), 10.0: dict(O=2e-3, g=1e-2), 30.0: dict(O=1e-2, g=2e-2)}
+
+
 @pytest.mark.parametrize("s", [1.0, 3.0, 10.0, 30.0])
 def test_logit_range_sweep(s, oracle):
-    """q and k multiplied by s (non-causal, stale mode): the running maximum moves by far more than 32 binades between
-    key tiles, so the lazy rescale of the forward fires; the kernel must stay on the emulation, whose own distance to
-    exact attention grows with s as the reference reports (O: 0.12 / 0.28 / 0.33 at s = 3 / 10 / 30)."""
-    B, N, H, Hk, D = 1, 2048, 4, 4, 128
+    """q and k multiplied by s (non-causal, stale mode) at the benchmark's size B=8 N=2048 H=Hk=16: the running maximum
+    moves by far more than 32 binades between key tiles, so the lazy rescale of the forward fires; the kernel must stay
+    on the emulation, whose own distance to exact attention grows with s as the reference reports (O: 0.12 / 0.28 /
+    0.33 at s = 3 / 10 / 30).  The emulation runs on two batches (memory); the kernel runs the whole configuration."""
+    B, N, H, Hk, D = 8, 2048, 16, 16, 128
     q, k, v, do = oracle.make_inputs(B, N, H, Hk, D, seed=8, device="cuda", qk_scale=s)
     got = run_ops(q, k, v, do, False, "stale")
-    em = oracle.dm_oracle(q, k, v, do, False, "stale", k_mean=got["kmean"], o_for_stale=got["O"])
-    ex = oracle.attention_exact(q, k, v, do, False)
     for nm in NAMES:
         assert torch.isfinite(got[nm].float()).all(), nm
-    e_c, e_e = oracle.rel_l2(got["O"], ex["O"]), oracle.rel_l2(em["O"], ex["O"])
-    record("sweep", f"s{s}", "O_vs_exact", e_c)
-    assert e_c <= 1.01 * e_e + 1e-5
-    # at s = 30 the logits reach thousands of log2 units, so fp32 rounding of S * c alone moves P by ~1e-3
-    assert oracle.rel_l2(got["O"], em["O"]) <= (2e-3 if s < 30 else 1e-2)
-    assert (got["LSE"] - em["LSE"]).abs().max().item() <= 1e-3 + 1e-5 * em["LSE"].abs().max().item()
-    bound = {1.0: 0.08, 3.0: 0.16, 10.0: 0.34, 30.0: 0.45}[s]
-    assert e_c < bound, (s, e_c)
-    for nm in ("dQ", "dK", "dV"):
-        d = oracle.rel_l2(got[nm], em[nm])
-        record("sweep", f"s{s}", nm, d)
-        assert d <= 2e-2, (nm, d)
+    gate = SWEEP_GATES[s]
+    for b0 in (0, B - 1):
+        sl = slice(b0, b0 + 1)
+        em = oracle.dm_oracle(q[sl], k[sl], v[sl], do[sl], False, "stale", k_mean=got["kmean"][sl], o_for_stale=got["O"][sl])
+        ex = oracle.attention_exact(q[sl], k[sl], v[sl], do[sl], False)
+        e_c, e_e = oracle.rel_l2(got["O"][sl], ex["O"]), oracle.rel_l2(em["O"], ex["O"])
+        record("sweep", f"s{s}_b{b0}", "O_vs_exact", e_c)
+        assert e_c <= 1.01 * e_e + 1e-5
+        d_o = oracle.rel_l2(got["O"][sl], em["O"])
+        record("sweep", f"s{s}_b{b0}", "O", d_o)
+        assert d_o <= gate["O"], ("O", s, d_o)
+        assert (got["LSE"][sl] - em["LSE"]).abs().max().item() <= 1e-3 + 1e-5 * em["LSE"].abs().max().item()
+        bound = {1.0: 0.08, 3.0: 0.16, 10.0: 0.34, 30.0: 0.45}[s]
+        assert e_c < bound, (s, e_c)
+        for nm in ("dQ", "dK", "dV"):
+            d = oracle.rel_l2(got[nm][sl], em[nm])
+            record("sweep", f"s{s}_b{b0}", nm, d)
+            assert d <= gate["g"], (nm, s, d)
 
 
 def test_long_context_unit(oracle):

@@ -56,3 +56,11 @@ def test_refuses_what_does_not_fit():
     assert rc < 0 and "built-in scratch" in err.value.decode()
     rc = L.dm_kmean_static(None, 8, 8, 128, 1, 128, 1, 128, ctypes.c_void_p(mean.data_ptr()), None, err, 512)
     assert rc < 0 and "NULL" in err.value.decode()
+    # a host pointer, or memory that is not CUDA memory, is refused before any launch
+    host = torch.zeros(1, 1, 128, 128, dtype=torch.bfloat16).pin_memory()
+    rc = L.dm_kmean_static(ctypes.c_void_p(host.data_ptr()), 8, 8, 128, 1, 128, 1, 128, ctypes.c_void_p(mean.data_ptr()),
+                           None, err, 512)
+    assert rc < 0 and "CUDA memory" in err.value.decode()
+    rc = L.dm_kmean_static(ctypes.c_void_p(k.data_ptr()), 8, 8, 128, 1, 128, 1, 128,
+                           ctypes.c_void_p(mean.data_ptr() + 4), None, err, 512)
+    assert rc < 0 and "aligned" in err.value.decode()
