@@ -369,8 +369,9 @@ def kernel_breakdown(job, steps):
     unit = 2.0 * 128 * 128 * D * tiles               # one matmul over every live tile
     two_pass = ws is not None
     hd256 = D == 256
-    # matmuls executed per tile: dK/dV kernel 4 (head_dim 256 without a workspace: 2 launches x 3), dQ 1 streaming / 3 recomputing
-    kernel_flops = {"forward": 2 * unit, "bwd_dkdv": (6 if (hd256 and not two_pass) else 4) * unit,
+    # matmuls executed per tile: dK/dV 4 (head_dim 256: a dV launch with S^T, dV and a dK launch with S^T, dP^T, dK = 5),
+    # dQ 1 streaming / 3 recomputing
+    kernel_flops = {"forward": 2 * unit, "bwd_dkdv": (5 if hd256 else 4) * unit,
                     "bwd_dq": (1 if two_pass else 3) * unit}
     if matched:
         kernel_flops["pass0_delta"] = 2 * unit

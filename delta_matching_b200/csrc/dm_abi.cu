@@ -293,7 +293,7 @@ static int bwd_impl(const void* q8, const void* k8, const void* v8, const void* 
   CUtensorMap tds;
   if (workspace != nullptr) {
     const int64_t need = dm_bwd_workspace_bytes(B, N, H, D);
-    if (need == 0) return fail(DM_ERR_ARG, "delta_matching: the dS workspace path needs head_dim 128 (got %d)", D);
+    if (need == 0) return fail(DM_ERR_ARG, "delta_matching: no dS workspace size for this shape (head_dim %d, seqlen %d)", D, N);
     if (workspace_bytes < need)
       return fail(DM_ERR_ARG, "delta_matching: dS workspace of %lld bytes given, %lld needed", (long long)workspace_bytes, (long long)need);
     DM_TRY(check_device_ptr(workspace, "workspace"));
@@ -311,7 +311,7 @@ static int bwd_impl(const void* q8, const void* k8, const void* v8, const void* 
     if (e != cudaSuccess) return cuda_fail(e, "backward dK/dV launch");
   }
   if (parts & 2) {
-    cudaError_t e = (workspace != nullptr) ? dm::launch_bwd_dq_p2(tds, tk, p, static_cast<cudaStream_t>(stream))
+    cudaError_t e = (workspace != nullptr) ? dm::launch_bwd_dq_p2(D, tds, tk, p, static_cast<cudaStream_t>(stream))
                                            : dm::launch_bwd_dq(D, tq, tk, tv, td, p, static_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) return cuda_fail(e, "backward dQ launch");
   }
@@ -319,7 +319,7 @@ static int bwd_impl(const void* q8, const void* k8, const void* v8, const void* 
 }
 
 int64_t dm_bwd_workspace_bytes(int B, int N, int H, int D) {
-  if (D != 128 || B <= 0 || H <= 0 || N <= 0 || (N % 128) != 0) return 0;
+  if ((D != 128 && D != 256) || B <= 0 || H <= 0 || N <= 0 || (N % 128) != 0) return 0;
   const int64_t tiles = static_cast<int64_t>(B) * H * (N / 128) * (N / 128);
   return tiles * (16384 + 4);
 }

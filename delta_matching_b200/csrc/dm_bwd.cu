@@ -62,14 +62,17 @@ struct KvCfg {
   static constexpr int kSmemQ = 2 * kTileBytes;                      // [kStages]
   static constexpr int kSmemDo = kSmemQ + kStages * kTileBytes;      // [kStages]
   static constexpr int kSmemVec = kSmemDo + kStages * kTileBytes;    // 2 x (l2[128], delta[128]) floats
-  static constexpr int kSmemBar = kSmemVec + 2 * 2 * 128 * 4;
+  static constexpr int kSmemWs = kSmemVec + 2 * 2 * 128 * 4;         // dS^T codes of the iteration for the workspace (DK)
+  static constexpr int kSmemBar = kSmemWs + (DK ? 16384 : 0);
   static constexpr int kSmemBytes = kSmemBar + 256 + 1024;
+  static_assert(kSmemBytes <= 232448, "shared memory budget");
 };
 
 template <int D, bool DV, bool DK>
 __global__ void __launch_bounds__(192, 1)
 bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do, const BwdParams p) {
+                const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
+                const __grid_constant__ CUtensorMap tm_ds, const BwdParams p) {
   using C = KvCfg<D, DV, DK>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -78,6 +81,9 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   uint8_t* sQ = smem + C::kSmemQ;
   uint8_t* sDo = smem + C::kSmemDo;
   float* sVec = reinterpret_cast<float*>(smem + C::kSmemVec);
+  uint8_t* sWs = smem + C::kSmemWs;
+  // the DK launch of the two-pass backward also leaves the dS^T codes in the workspace (pass 2 computes dQ from them)
+  const bool ws = DK && p.ds_codes != nullptr;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kSmemBar);
   uint64_t* bar_kv = bars + 0;
   uint64_t* bar_s = bars + 1;       // S^T, dP^T ready
@@ -192,9 +198,20 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                           (it > 0) || (ks > 0));
           }
         }
+        if (ws) {
+          // the compute warps left the dS^T codes of this iteration in the staging tile: send it to the workspace.  The
+          // store has read the tile before bar_done is committed, which is what the warps wait for before the next
+          // iteration's codes.
+          const int hq_it = hk * rep + it / n_qi, qt_it = qt0 + it % n_qi;
+          const int ws_tile = ((b * p.H + hq_it) * n_t + qt_it) * n_t + kt;
+          tma_store_2d(&tm_ds, sWs, 0, ws_tile * 128);
+          bulk_commit_group();
+          bulk_wait_group_read<0>();
+        }
         tc_commit(empty + st);
         tc_commit(bar_done);
       }
+      if (ws) bulk_wait_group<0>();
       if (!ok) raise_abort(abort_flag, p.status, kStatusTimeoutMma);
     }
   } else {
@@ -281,10 +298,23 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             codes[e / 4] = cvt_e4m3x4(ds[32 * c + e] * inv, ds[32 * c + e + 1] * inv, ds[32 * c + e + 2] * inv,
                                       ds[32 * c + e + 3] * inv);
           tmem_st8(tmem + lane_base + C::kColDp + 8 * c, codes);
+          if (ws) {
+            // the same codes as row `tid` of a [key][query] tile in 128-byte-swizzled shared memory (16-byte chunk j at
+            // chunk j ^ (tid % 8)): the layout pass 2 reads as an MN-major A operand
+            sts_u4(sWs + tid * 128 + (((2 * c) ^ (tid & 7)) << 4), codes[0], codes[1], codes[2], codes[3]);
+            sts_u4(sWs + tid * 128 + (((2 * c + 1) ^ (tid & 7)) << 4), codes[4], codes[5], codes[6], codes[7]);
+          }
         }
         const uint32_t w = pack4(sb_mul(dsb, scale_to_sb(qsv[0])), sb_mul(dsb, scale_to_sb(qsv[1])),
                                  sb_mul(dsb, scale_to_sb(qsv[2])), sb_mul(dsb, scale_to_sb(qsv[3])));
         tmem_st4(tmem + lane_base + C::kColSfaK, w, w, w, w);
+        if (ws) {
+          fence_async_smem();
+          if ((tid & 31) == 0) {
+            const size_t ws_tile = (static_cast<size_t>(bh) * n_t + qt) * n_t + kt;
+            p.ds_words[ws_tile * 4 + warp] = static_cast<uint8_t>(dsb);
+          }
+        }
       }
       tmem_wait_st();
       tc_fence_before();
@@ -1735,13 +1765,13 @@ static cudaError_t set_smem(K kernel, int bytes, bool* done) {
 
 template <int D, bool DV, bool DK>
 static cudaError_t launch_kv_t(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
-                               const CUtensorMap& tdo, const BwdParams& p, cudaStream_t stream) {
+                               const CUtensorMap& tdo, const CUtensorMap& tds, const BwdParams& p, cudaStream_t stream) {
   using C = KvCfg<D, DV, DK>;
   static bool done[64] = {};
   cudaError_t e = set_smem(bwd_dkdv_kernel<D, DV, DK>, C::kSmemBytes, done);
   if (e != cudaSuccess) return e;
   dim3 grid(p.N / 128, p.B * p.Hk);
-  bwd_dkdv_kernel<D, DV, DK><<<grid, 192, C::kSmemBytes, stream>>>(tq, tk, tv, tdo, p);
+  bwd_dkdv_kernel<D, DV, DK><<<grid, 192, C::kSmemBytes, stream>>>(tq, tk, tv, tdo, tds, p);
   count_launch();
   return cudaGetLastError();
 }
@@ -1785,9 +1815,9 @@ cudaError_t launch_bwd_dkdv(int D, const CUtensorMap& tq, const CUtensorMap& tk,
     return cudaGetLastError();
   }
   // head_dim 256: S^T + dP^T + dK + dV exceed the 512 TMEM columns, so dV and dK run as two launches
-  cudaError_t e = launch_kv_t<256, true, false>(tq, tk, tv, tdo, p, stream);
+  cudaError_t e = launch_kv_t<256, true, false>(tq, tk, tv, tdo, *tds, p, stream);
   if (e != cudaSuccess) return e;
-  return launch_kv_t<256, false, true>(tq, tk, tv, tdo, p, stream);
+  return launch_kv_t<256, false, true>(tq, tk, tv, tdo, *tds, p, stream);
 }
 
 template <int D>

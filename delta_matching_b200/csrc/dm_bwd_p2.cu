@@ -1,4 +1,4 @@
-// Backward pass 2 (head_dim 128): dQ = dS K from the quantised dS tiles that the dK / dV kernel left in a workspace.
+// Backward pass 2: dQ = dS K from the quantised dS tiles that the dK / dV kernel left in a workspace.
 //
 // Reference structure: pass 1 writes dS codes, pass 2 multiplies them with K
 // (csrc/fq8_dq_pass2_hd128.h:407-442, launched from csrc/flash_bwd_fp8v10_launch.h:158-163).  The alternative without a
@@ -11,8 +11,9 @@
 // (M = queries contiguous); K is the B operand in MN-major form as in the other kernels.
 //
 // One persistent CTA per SM, 320 threads: warps 0-3 write the per-tile scale words into TMEM (byte j = dS scale x K
-// scale of key block j, identical for all 128 rows), warps 4-7 write dQ out (two accumulators alternate between
-// items), warp 8 TMA, warp 9 MMA.  Items = (query tile, head), most key tiles first.
+// scale of key block j, identical for all 128 rows), warps 4-7 write dQ out (at head_dim 128 two accumulators alternate
+// between items; at head_dim 256 one accumulator fills the columns, and an item's first chain waits for the read-out
+// of the previous item), warp 8 TMA, warp 9 MMA.  Items = (query tile, head), most key tiles first.
 #include <cuda_bf16.h>
 #include "dm_common.cuh"
 #include "dm_kernels.h"
@@ -20,23 +21,29 @@
 
 namespace dm {
 
+template <int D>
 struct DqP2Cfg {
-  static constexpr int kTileBytes = 128 * 128;
-  static constexpr int kStages = 7;            // dS^T tile + K tile + scale word per stage (7 x 32 KiB of the 227 KiB)
+  static constexpr int kSub = D / 128;           // 128-byte-wide sub-tiles of a K row
+  static constexpr int kDsBytes = 128 * 128;     // dS^T tile
+  static constexpr int kKBytes = 128 * D;        // K tile
+  static constexpr int kStages = (D == 128) ? 7 : 4;   // dS^T tile + K tile + scale word per stage (224 / 192 KiB)
+  static constexpr int kAccs = (D == 128) ? 2 : 1;     // dQ accumulators of D fp32 columns
   static constexpr int kThreads = 320;
   static constexpr int kTmemCols = 512;
-  static constexpr int kColDq = 0;             // 2 x 128 fp32 columns
+  static constexpr int kColDq = 0;
   static constexpr int kColSf = 256;           // kStages x 4 columns: the tile's scale word
   static constexpr int kColOne = 256 + 4 * kStages;   // 4 columns of 0x7F7F7F7F: scale 1.0 for the B operand
   static constexpr int kSmemDs = 0;
-  static constexpr int kSmemK = kStages * kTileBytes;
-  static constexpr int kSmemBar = 2 * kStages * kTileBytes;
+  static constexpr int kSmemK = kStages * kDsBytes;
+  static constexpr int kSmemBar = kStages * (kDsBytes + kKBytes);
   static constexpr int kSmemBytes = kSmemBar + 256 + 1024;
+  static_assert(kSmemBytes <= 232448, "shared memory budget");
 };
 
-__global__ void __launch_bounds__(DqP2Cfg::kThreads, 1)
+template <int D>
+__global__ void __launch_bounds__(DqP2Cfg<D>::kThreads, 1)
 bwd_dq_p2_kernel(const __grid_constant__ CUtensorMap tm_ds, const __grid_constant__ CUtensorMap tm_k, const BwdParams p) {
-  using C = DqP2Cfg;
+  using C = DqP2Cfg<D>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sDs = smem + C::kSmemDs;
@@ -97,9 +104,10 @@ bwd_dq_p2_kernel(const __grid_constant__ CUtensorMap tm_ds, const __grid_constan
         for (int it = 0; it < n_it; ++it, ++g) {
           const uint32_t st = g % C::kStages;
           if (g >= C::kStages && !(ok = wait_or_abort(empty + st, ((g / C::kStages) - 1) & 1, abort_flag))) break;
-          mbar_expect_tx(full + st, 2 * C::kTileBytes);
-          tma_load_2d(sDs + st * C::kTileBytes, &tm_ds, full + st, 0, (tile0 + it) * 128);
-          tma_load_2d(sK + st * C::kTileBytes, &tm_k, full + st, 0, bhk * p.N + it * 128);
+          mbar_expect_tx(full + st, C::kDsBytes + C::kKBytes);
+          tma_load_2d(sDs + st * C::kDsBytes, &tm_ds, full + st, 0, (tile0 + it) * 128);
+          for (int sub = 0; sub < C::kSub; ++sub)
+            tma_load_2d(sK + st * C::kKBytes + sub * 16384, &tm_k, full + st, sub * 128, bhk * p.N + it * 128);
         }
       }
       if (!ok) raise_abort(abort_flag, p.status, kStatusTimeoutProducer);
@@ -113,21 +121,24 @@ bwd_dq_p2_kernel(const __grid_constant__ CUtensorMap tm_ds, const __grid_constan
       for (int k = 0, item; ok && (item = sched_item(k, first_item, item_step)) < n_items; ++k, ++n_done) {
         const int qt = n_t - 1 - item / BH;
         const int n_it = p.causal ? (qt + 1) : n_t;
-        const uint32_t acc = n_done & 1;
-        // the accumulator was last used two items ago: its read-out must be complete
-        if (n_done >= 2 && !(ok = wait_or_abort(dq_free + acc, ((n_done >> 1) - 1) & 1, abort_flag))) break;
+        const uint32_t acc = n_done % C::kAccs;
+        // the accumulator was last used kAccs items ago: its read-out must be complete
+        if (n_done >= C::kAccs && !(ok = wait_or_abort(dq_free + acc, ((n_done / C::kAccs) - 1) & 1, abort_flag))) break;
         for (int it = 0; it < n_it; ++it, ++g) {
           const uint32_t st = g % C::kStages;
           if (!(ok = wait_or_abort(full + st, (g / C::kStages) & 1, abort_flag))) break;
           tc_fence_after();
           // dQ += dS K over the tile's 128 keys: A = dS^T tile read MN-major, B = K tile read MN-major; both advance
           // by 32 key rows (4096 bytes) per step; byte ks of the scale word belongs to key block ks
-          const uint32_t ds_lo = ds_lo0 + st * (C::kTileBytes >> 4), k_lo = k_lo0 + st * (C::kTileBytes >> 4);
+          const uint32_t ds_lo = ds_lo0 + st * (C::kDsBytes >> 4), k_lo = k_lo0 + st * (C::kKBytes >> 4);
 #pragma unroll
-          for (int ks = 0; ks < 4; ++ks)
-            mma_mxf8_ss(tmem + C::kColDq + 128 * acc, ds_lo + ks * 256, k_lo + ks * 256,
-                        idesc_mxf8(128, 128, true, true, ks, 0), tmem + C::kColSf + 4 * st, tmem + C::kColOne,
-                        (it > 0) || (ks > 0));
+          for (int ks = 0; ks < 4; ++ks) {
+#pragma unroll
+            for (int sub = 0; sub < C::kSub; ++sub)
+              mma_mxf8_ss(tmem + C::kColDq + D * acc + 128 * sub, ds_lo + ks * 256, k_lo + sub * 1024 + ks * 256,
+                          idesc_mxf8(128, 128, true, true, ks, 0), tmem + C::kColSf + 4 * st, tmem + C::kColOne,
+                          (it > 0) || (ks > 0));
+          }
           tc_commit(empty + st);
           if (it == n_it - 1) tc_commit(dq_full + acc);
         }
@@ -217,15 +228,15 @@ bwd_dq_p2_kernel(const __grid_constant__ CUtensorMap tm_ds, const __grid_constan
     for (int k = 0, item; ok && (item = sched_item(k, first_item, item_step)) < n_items; ++k, ++n_done) {
       const int qt = n_t - 1 - item / BH, bh = item % BH;
       const int b = bh / p.H, h = bh % p.H;
-      const uint32_t acc = n_done & 1;
-      if (!(ok = wait_warp(dq_full + acc, (n_done >> 1) & 1, abort_flag))) break;
+      const uint32_t acc = n_done % C::kAccs;
+      if (!(ok = wait_warp(dq_full + acc, (n_done / C::kAccs) & 1, abort_flag))) break;
       tc_fence_after();
       __nv_bfloat16* dst = p.dq + static_cast<int64_t>(b) * p.dq_sb + static_cast<int64_t>(qt * 128 + r) * p.dq_sn +
                            static_cast<int64_t>(h) * p.dq_sh;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < D / 32; ++c) {
         uint32_t rr[32];
-        tmem_ld32(tmem + lane_base + C::kColDq + 128 * acc + 32 * c, rr);
+        tmem_ld32(tmem + lane_base + C::kColDq + D * acc + 32 * c, rr);
         tmem_wait_ld();
         uint32_t w[16];
 #pragma unroll
@@ -249,14 +260,15 @@ bwd_dq_p2_kernel(const __grid_constant__ CUtensorMap tm_ds, const __grid_constan
   if (warp == 9) tmem_dealloc(tmem, C::kTmemCols);
 }
 
-cudaError_t launch_bwd_dq_p2(const CUtensorMap& tds, const CUtensorMap& tk, const BwdParams& p, cudaStream_t stream) {
-  using C = DqP2Cfg;
+template <int D>
+static cudaError_t launch_p2_t(const CUtensorMap& tds, const CUtensorMap& tk, const BwdParams& p, cudaStream_t stream) {
+  using C = DqP2Cfg<D>;
   static bool attr_set[64] = {};
   static int sm_count[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(bwd_dq_p2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+    cudaError_t e = cudaFuncSetAttribute(bwd_dq_p2_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
     if (e != cudaSuccess) return e;
     e = cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev);
     if (e != cudaSuccess) return e;
@@ -264,9 +276,13 @@ cudaError_t launch_bwd_dq_p2(const CUtensorMap& tds, const CUtensorMap& tk, cons
   }
   const int sms = (dev >= 0 && dev < 64) ? sm_count[dev] : 148;
   const int items = (p.N / 128) * p.B * p.H;
-  bwd_dq_p2_kernel<<<items < sms ? items : sms, C::kThreads, C::kSmemBytes, stream>>>(tds, tk, p);
+  bwd_dq_p2_kernel<D><<<items < sms ? items : sms, C::kThreads, C::kSmemBytes, stream>>>(tds, tk, p);
   count_launch();
   return cudaGetLastError();
+}
+
+cudaError_t launch_bwd_dq_p2(int D, const CUtensorMap& tds, const CUtensorMap& tk, const BwdParams& p, cudaStream_t stream) {
+  return D == 128 ? launch_p2_t<128>(tds, tk, p, stream) : launch_p2_t<256>(tds, tk, p, stream);
 }
 
 }  // namespace dm

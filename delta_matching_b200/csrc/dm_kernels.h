@@ -48,7 +48,7 @@ struct BwdParams {
   int64_t dv_sb, dv_sn, dv_sh;
   float* rowsum_ds;            // optional (B, H, N): sum_j dS_ij before quantisation (identity probe); may be null
   float* sum_abs_pdp;          // optional (B, H, N): sum_j |P_ij dP_ij|; may be null
-  uint8_t* ds_codes;           // optional dS workspace (head_dim 128): tile (bh, qt, kt) at ((bh n_t + qt) n_t + kt) x 16384
+  uint8_t* ds_codes;           // optional dS workspace: tile (bh, qt, kt) at ((bh n_t + qt) n_t + kt) x 16384
   uint8_t* ds_words;           // bytes, [key][query] e4m3 codes; then per tile 4 UE8M0 bytes (one per 32-key block)
   float sm_scale;
   int B, H, Hk, N;
@@ -90,7 +90,7 @@ cudaError_t launch_bwd_dkdv(int D, const CUtensorMap& tq, const CUtensorMap& tk,
                             cudaStream_t stream);
 cudaError_t launch_bwd_dq(int D, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                           const CUtensorMap& tdo, const BwdParams& p, cudaStream_t stream);
-cudaError_t launch_bwd_dq_p2(const CUtensorMap& tds, const CUtensorMap& tk, const BwdParams& p, cudaStream_t stream);
+cudaError_t launch_bwd_dq_p2(int D, const CUtensorMap& tds, const CUtensorMap& tk, const BwdParams& p, cudaStream_t stream);
 cudaError_t launch_quant(const QuantParams& p, cudaStream_t stream);
 cudaError_t launch_kmean(const KMeanParams& p, cudaStream_t stream);
 

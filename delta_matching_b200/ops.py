@@ -238,7 +238,7 @@ def delta_fp8(q8, k8, v8, do8, qs, ks, vs, dos, lse, causal: bool):
 
 
 def bwd_workspace_bytes(B: int, N: int, H: int, D: int) -> int:
-    """Bytes of the dS workspace of the two-pass backward (0: the path does not apply, head_dim != 128)."""
+    """Bytes of the dS workspace of the two-pass backward (0: the shape is not one the kernels take)."""
     return int(_lib.lib().dm_bwd_workspace_bytes(int(B), int(N), int(H), int(D)))
 
 
@@ -282,8 +282,8 @@ def bwd_fp8(q8, k8, v8, do8, qs, ks, vs, dos, lse, delta, causal: bool, identity
     quantised.  parts: 1 = only the dK / dV kernel, 2 = only the dQ kernel, 3 = both (the outputs of a kernel that did
     not run are uninitialised).  Replaces the bwd_fp8_t op and the group fold of delta_matching/attn.py:114-117.
 
-    head_dim 128 without the identity probe runs the two-pass form: the dK / dV kernel leaves the dS codes in a
-    workspace and dQ streams them (bit-identical to the recomputing kernel).  The workspace is allocated here unless
+    Without the identity probe the two-pass form runs: the dK / dV kernel leaves the dS codes in a workspace and dQ
+    streams them (bit-identical to the recomputing kernel).  The workspace is allocated here unless
     `workspace` (uint8, at least bwd_workspace_bytes) is given; when it would exceed DM_BWD_WORKSPACE_MB the call is
     split over (batch, kv-head group) ranges, and when a single group exceeds it the recomputing kernel runs."""
     dev = _cuda(q8, k8, v8, do8, qs, ks, vs, dos, lse, delta)
@@ -298,7 +298,7 @@ def bwd_fp8(q8, k8, v8, do8, qs, ks, vs, dos, lse, delta, causal: bool, identity
     n_t = N // 128
     cap = _workspace_cap_bytes(dev)
     group_bytes = bwd_workspace_bytes(1, N, rep, D)
-    two_pass = (D == 128 and not identity and group_bytes > 0 and (workspace is not None or group_bytes <= cap)
+    two_pass = (not identity and group_bytes > 0 and (workspace is not None or group_bytes <= cap)
                 and rep * n_t * n_t <= _MAX_WS_TILES)
     with torch.cuda.device(dev):
         dq = torch.empty(B, N, H, D, device=dev, dtype=torch.bfloat16)

@@ -122,16 +122,17 @@ int dm_bwd_parts(const void* q8, const void* k8, const void* v8, const void* do8
                  void* dv, int64_t dv_sb, int64_t dv_sn, int64_t dv_sh,
                  float* rowsum_ds, float* sum_abs_pdp, int parts, int* status, void* stream);
 
-/* The backward in the reference's two-pass form, for head_dim 128: the dK / dV kernel (pass 1) also leaves the quantised
- * dS tiles in `workspace`, and dQ = dS K is a streaming kernel over them (pass 2) instead of a kernel that recomputes S,
- * dP and the exponentials (csrc/flash_bwd_fp8v10_launch.h:158-163, csrc/fq8_dq_pass2_hd128.h:407-442; the reference
- * allocates the dS buffer inside the op and bounds it with its head-group split, delta_matching/attn.py:88-112,
- * delta_matching/split.py:37-97).
+/* The backward in the reference's two-pass form: the dK / dV kernel (pass 1) also leaves the quantised dS tiles in
+ * `workspace`, and dQ = dS K is a streaming kernel over them (pass 2) instead of a kernel that recomputes S, dP and the
+ * exponentials (csrc/flash_bwd_fp8v10_launch.h:158-163, csrc/fq8_dq_pass2_hd128.h:407-442; the reference allocates the
+ * dS buffer inside the op and bounds it with its head-group split, delta_matching/attn.py:88-112,
+ * delta_matching/split.py:37-97; its Blackwell head_dim-256 route has the same two kernels,
+ * delta_matching/sm100/attention_bwd_hd256_sm100.py:1-10).
  * Outputs are bit-identical to dm_bwd.  workspace: device buffer of at least dm_bwd_workspace_bytes(B, N, H, D) bytes,
  * 16-byte aligned; contents on entry are ignored.  parts as in dm_bwd_parts; parts = 2 alone reads what an earlier
  * parts = 1 call with the same arguments wrote.  Limit: B * H * (N / 128)^2 < 2^24 tiles per call (split the heads
  * beyond that).  There is no identity probe on this path (use dm_bwd). */
-int64_t dm_bwd_workspace_bytes(int B, int N, int H, int D);     /* 0 when the path does not apply (D != 128) */
+int64_t dm_bwd_workspace_bytes(int B, int N, int H, int D);     /* 0 for a shape the kernels do not take */
 int dm_bwd_ws(const void* q8, const void* k8, const void* v8, const void* do8,
               const float* qs, const float* ks, const float* vs, const float* dos,
               const float* lse, const float* delta,

@@ -9,8 +9,8 @@ pytestmark = pytest.mark.gpu
 NAMES = ("dQ", "dK", "dV")
 
 
-def _bwd(oracle, monkeypatch, cap_mb, B, N, H, Hk, causal, mode, seed):
-    q, k, v, do = oracle.make_inputs(B, N, H, Hk, 128, seed=seed, device="cuda")
+def _bwd(oracle, monkeypatch, cap_mb, B, N, H, Hk, causal, mode, seed, D=128):
+    q, k, v, do = oracle.make_inputs(B, N, H, Hk, D, seed=seed, device="cuda")
     if cap_mb is None:
         monkeypatch.delenv("DM_BWD_WORKSPACE_MB", raising=False)
     else:
@@ -23,6 +23,14 @@ def _bwd(oracle, monkeypatch, cap_mb, B, N, H, Hk, causal, mode, seed):
 def test_two_pass_equals_recompute(B, N, H, Hk, causal, mode, oracle, monkeypatch):
     ref = _bwd(oracle, monkeypatch, 0, B, N, H, Hk, causal, mode, seed=31)            # 0: recomputing kernel
     got = _bwd(oracle, monkeypatch, None, B, N, H, Hk, causal, mode, seed=31)         # default: two-pass
+    for nm in NAMES:
+        assert torch.equal(got[nm], ref[nm]), nm
+
+
+@pytest.mark.parametrize("B,N,H,Hk,causal,mode", [(1, 512, 4, 2, True, "matched"), (2, 384, 2, 2, False, "stale")])
+def test_two_pass_equals_recompute_hd256(B, N, H, Hk, causal, mode, oracle, monkeypatch):
+    ref = _bwd(oracle, monkeypatch, 0, B, N, H, Hk, causal, mode, seed=34, D=256)
+    got = _bwd(oracle, monkeypatch, None, B, N, H, Hk, causal, mode, seed=34, D=256)
     for nm in NAMES:
         assert torch.equal(got[nm], ref[nm]), nm
 
@@ -56,4 +64,5 @@ def test_parts_share_a_workspace(oracle):
 def test_workspace_bytes():
     from delta_matching_b200 import ops
     assert ops.bwd_workspace_bytes(4, 4096, 32, 128) == 4 * 32 * 32 * 32 * (16384 + 4)
-    assert ops.bwd_workspace_bytes(2, 1024, 4, 256) == 0
+    assert ops.bwd_workspace_bytes(2, 1024, 4, 256) == 2 * 4 * 8 * 8 * (16384 + 4)      # the tile does not depend on head_dim
+    assert ops.bwd_workspace_bytes(2, 1000, 4, 128) == 0
