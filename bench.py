@@ -329,15 +329,16 @@ def validate_units(job, world, rank):
     return out
 
 
-def kernel_breakdown(job, steps):
+def kernel_breakdown(job, steps, first_units=None):
     """Each kernel of the step timed alone (CUDA events, same stream), and its roofline: tensor kernels by executed
     matmul FLOPs against 2 x the measured bf16 burst rate, HBM kernels by algorithmic bytes against the measured copy
-    bandwidth."""
+    bandwidth.  first_units: take only that many leading batch entries of the rank's inputs (long-context shards)."""
     from delta_matching_b200 import ops
     w, dev = job.w, job.dev
     stream = torch.cuda.current_stream()
     causal, matched = w["causal"], w["mode"] == "matched"
-    qh, kh, vh, doh = (x.transpose(1, 2) for x in (job.q, job.k, job.v, job.do))
+    src = (job.q, job.k, job.v, job.do) if first_units is None else tuple(t[:first_units] for t in (job.q, job.k, job.v, job.do))
+    qh, kh, vh, doh = (x.transpose(1, 2) for x in src)
     q8, qs, k8, ks, v8, vs, _ = ops.quant_qkv(qh, kh, vh)
     o, lse = ops.fwd_fp8(q8, k8, v8, qs, ks, vs, causal)
     if matched:
@@ -549,10 +550,11 @@ def main():
     validation = validate_units(job, world, rank) if job.sharded else None
 
     small = job.input_bytes() <= (2 << 30)
-    kernel_ms = roofline = rooflines = None
-    executed = None
-    if small:
-        kernel_ms, roofline, rooflines, executed = kernel_breakdown(job, args.steps)
+    # per-kernel times: on the whole workload when it is small, else on the rank's first (batch, kv-group) unit
+    kernel_ms, roofline, rooflines, executed = kernel_breakdown(job, min(args.steps, 10) if not small else args.steps,
+                                                                 first_units=None if small else 1)
+    if not small:
+        roofline["scope"] = "one (batch, kv-group) unit of the shard, timed alone"
     sustained = None
     if small and world == 1 and not args.no_extra:
         sustained = sustained_leg(job, 2.5, ms, local, executed)

@@ -767,8 +767,8 @@ bwd_dkdv_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
 struct KvTeamCfg {
   static constexpr int kTileBytes = 128 * 128;
   static constexpr int kStages = 4;
-  static constexpr int kWarps = 16;          // compute warps; warp 16 = TMA, warp 17 = MMA, warps 18-19 only fill the
-  static constexpr int kThreads = kWarps * 32 + 128;   // fifth warpgroup, so that it can hand registers to the other four
+  static constexpr int kWarps = 16;          // compute warps; warp 16 = TMA, warp 17 = MMA
+  static constexpr int kThreads = kWarps * 32 + 64;
   static constexpr int kTmemCols = 512;
   static constexpr int kColSd = 0;           // team t: columns [64 t, 64 t + 64): S^T, then dP^T (fp32)
   static constexpr int kColPc = 128;         // P^T codes: 8 columns per 32-query block
@@ -861,13 +861,7 @@ bwd_dkdv_team_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
 
-  // The compute warps keep 64 fp32 values per thread across their waits; the TMA and MMA threads need few registers:
-  // the fifth warpgroup hands registers to the other four (each branch below starts with its side of the hand-over).
-  if (warp >= kW) {
-    reg_dealloc<64>();                                 // one instruction for the whole warpgroup; warps 18-19 do nothing else
-  }
-  if (warp >= kW + 2) {
-  } else if (warp == kW) {
+  if (warp == kW) {
     // ------------------------------------------------------------------------------------------ TMA producer
     if (elect_one()) {
       tma_prefetch_desc(&tm_q);
@@ -990,7 +984,6 @@ bwd_dkdv_team_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     }
   } else {
     // ------------------------------------------------------------------------------------------ compute teams
-    reg_alloc<104>();
     const int team = warp >> 3;
     const int wg = warp >> 2;                          // 32-query block of every tile (blocks 2 team, 2 team + 1)
     const int quad = warp & 3;                         // lane quadrant = 32-key block of the dS scale

@@ -23,17 +23,6 @@ __device__ __forceinline__ bool elect_one() {
   return pred != 0;
 }
 
-// Per-warpgroup register budget (setmaxnreg): every warp of a 128-thread group executes the same call.  A group that
-// needs few registers releases them, the others may then grow beyond what the launch allotted to every thread.
-template <int N>
-__device__ __forceinline__ void reg_dealloc() {
-  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
-}
-template <int N>
-__device__ __forceinline__ void reg_alloc() {
-  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
-}
-
 // ------------------------------------------------------------------------------------------------ mbarrier
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");

@@ -242,11 +242,15 @@ def bwd_workspace_bytes(B: int, N: int, H: int, D: int) -> int:
     return int(_lib.lib().dm_bwd_workspace_bytes(int(B), int(N), int(H), int(D)))
 
 
-def _workspace_cap_bytes(device=None) -> int:
+_SMALL_WS = 4 << 30
+
+
+def _workspace_cap_bytes(device=None, need: int = 0) -> int:
     """Bound of the dS workspace of one backward call: DM_BWD_WORKSPACE_MB (MiB; 0 selects the backward that recomputes
     instead of storing), else the reference's own knob DM_BWD_WS_LIMIT_GB (delta_matching/split.py:37-97 bounds the same
-    buffer by splitting the call per head group), else 60 % of the device memory that is free or held idle by torch's
-    caching allocator (at least 4 GiB), so that on a 180 GB GPU many (batch, kv-group) units share one launch."""
+    buffer by splitting the call per head group), else 4 GiB when the whole call needs no more than that (no query of the
+    device: the common training shapes stay on this path), else 60 % of the device memory that is free or held idle by
+    torch's caching allocator, so that on a 180 GB GPU many (batch, kv-group) units of a long context share one launch."""
     try:
         if "DM_BWD_WORKSPACE_MB" in os.environ:
             return int(os.environ["DM_BWD_WORKSPACE_MB"]) << 20
@@ -254,11 +258,13 @@ def _workspace_cap_bytes(device=None) -> int:
             return int(float(os.environ["DM_BWD_WS_LIMIT_GB"]) * (1 << 30))
     except ValueError:
         pass
+    if need <= _SMALL_WS:
+        return _SMALL_WS
     if device is None or torch.cuda.is_current_stream_capturing():
         return 16384 << 20
     free, _ = torch.cuda.mem_get_info(device)
     idle = torch.cuda.memory_reserved(device) - torch.cuda.memory_allocated(device)
-    return max(4 << 30, int(0.6 * (free + idle)))
+    return max(_SMALL_WS, int(0.6 * (free + idle)))
 
 
 _MAX_WS_TILES = (1 << 24) - 1
@@ -296,8 +302,8 @@ def bwd_fp8(q8, k8, v8, do8, qs, ks, vs, dos, lse, delta, causal: bool, identity
     L = _lib.lib()
     rep = H // Hk
     n_t = N // 128
-    cap = _workspace_cap_bytes(dev)
     group_bytes = bwd_workspace_bytes(1, N, rep, D)
+    cap = _workspace_cap_bytes(dev, group_bytes * B * Hk)
     two_pass = (not identity and group_bytes > 0 and (workspace is not None or group_bytes <= cap)
                 and rep * n_t * n_t <= _MAX_WS_TILES)
     with torch.cuda.device(dev):
