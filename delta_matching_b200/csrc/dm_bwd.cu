@@ -16,7 +16,6 @@
 //              dQ's scale along keys = ds_sb (+) ks_sb;  dQ = (dS K) * D^-0.5.
 // Both kernels evaluate P and dS with the same operations on the same accumulators, so the dS codes of kernel 2 are the
 // codes of kernel 1 whenever the two MMA orientations return the same fp32 sums.
-#include <cstdlib>
 #include <cuda_bf16.h>
 #include "dm_common.cuh"
 #include "dm_kernels.h"
@@ -749,428 +748,6 @@ bwd_dkdv_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   if (warp == kW + 1) tmem_dealloc(tmem, C::kTmemCols);
 }
 
-// ================================================================================================ dK / dV, two teams (D = 128)
-// One CTA per SM and (key tile, kv head, batch); 16 compute warps in two teams of eight, then one TMA warp and one MMA
-// warp.  Team t owns the queries [64 t, 64 t + 64) of every 128-query tile (warp = (32-key lane quadrant, 32-query
-// block); thread = one key row x 32 queries), its own 64 TMEM columns that S^T and then dP^T of its half pass through,
-// and its own code and scale-word columns.  The single MMA thread serves the two teams in a fixed interleaved order, which
-// keeps them half a tile apart: while one team takes exponentials (MUFU pipe) the other does the dS arithmetic and the
-// e4m3 conversions (FMA / ALU pipes), and the tensor pipe runs the other team's chains behind both.
-//
-// The dS scale is one power of two per (128 queries x 32 keys), i.e. it spans both teams.  A team therefore keeps the
-// dS values of tile i in registers, publishes its block maxima, carries on with the exponentials of tile i + 1 and
-// converts dS(i) afterwards, when the other team's maxima of tile i have long been published: nobody waits for the
-// other team inside a tile.
-//
-// The order in which chains are issued into the dV and dK accumulators is fixed by the MMA thread's program
-// (dV: A(0) B(0) A(1) B(1) ...; dK the same), so the results do not depend on timing.
-struct KvTeamCfg {
-  static constexpr int kTileBytes = 128 * 128;
-  static constexpr int kStages = 4;
-  static constexpr int kWarps = 16;          // compute warps; warp 16 = TMA, warp 17 = MMA
-  static constexpr int kThreads = kWarps * 32 + 64;
-  static constexpr int kTmemCols = 512;
-  static constexpr int kColSd = 0;           // team t: columns [64 t, 64 t + 64): S^T, then dP^T (fp32)
-  static constexpr int kColPc = 128;         // P^T codes: 8 columns per 32-query block
-  static constexpr int kColDc = 160;         // dS^T codes
-  static constexpr int kColXv = 192;         // 4 x 4 columns: dV scale word of query block b (byte 0)
-  static constexpr int kColXk = 208;         // 4 x 4 columns: dK scale word of query block b
-  static constexpr int kColOne = 224;        // 4 columns of 0x7F7F7F7F
-  static constexpr int kColDv = 256, kColDk = 384;
-  static constexpr int kSmemK = 0;
-  static constexpr int kSmemV = kTileBytes;
-  static constexpr int kSmemQ = 2 * kTileBytes;                      // [kStages]
-  static constexpr int kSmemDo = kSmemQ + kStages * kTileBytes;      // [kStages]
-  static constexpr int kSmemVec = kSmemDo + kStages * kTileBytes;    // [kStages] x (lse[128], delta[128]) floats
-  static constexpr int kSmemWs = kSmemVec + kStages * 1024;          // 2 staging tiles of dS^T codes for the workspace
-  static constexpr int kSmemXch = kSmemWs + 2 * kTileBytes;          // 2 x [16 warps] block maxima
-  static constexpr int kSmemBar = kSmemXch + 2 * 16 * 4;
-  static constexpr int kSmemBytes = kSmemBar + 256 + 1024;
-};
-
-__global__ void __launch_bounds__(KvTeamCfg::kThreads, 1)
-bwd_dkdv_team_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                     const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
-                     const __grid_constant__ CUtensorMap tm_ds, const BwdParams p) {
-  using C = KvTeamCfg;
-  constexpr int kW = C::kWarps;
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* sK = smem + C::kSmemK;
-  uint8_t* sV = smem + C::kSmemV;
-  uint8_t* sQ = smem + C::kSmemQ;
-  uint8_t* sDo = smem + C::kSmemDo;
-  float* sVec = reinterpret_cast<float*>(smem + C::kSmemVec);
-  float* sXch = reinterpret_cast<float*>(smem + C::kSmemXch);
-  uint8_t* sWs = smem + C::kSmemWs;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kSmemBar);
-  uint64_t* bar_kv = bars + 0;
-  uint64_t* bar_s = bars + 1;        // [2] S^T of the team's half landed (MMA commit)
-  uint64_t* bar_sfree = bars + 3;    // [2] every warp of the team holds its S^T columns (one arrival per warp)
-  uint64_t* bar_dp = bars + 5;       // [2] dP^T of the half landed
-  uint64_t* bar_dpfree = bars + 7;   // [2] every warp of the team holds its dP^T columns
-  uint64_t* bar_pv = bars + 9;       // [2] P^T codes + dV scale words of the half written
-  uint64_t* bar_pk = bars + 11;      // [2] dS^T codes + dK scale words of the half written
-  uint64_t* bar_dv = bars + 13;      // [2] the team's dV chain is done (its codes and words may be replaced)
-  uint64_t* bar_dk = bars + 15;      // [2] the team's dK chain is done
-  uint64_t* bar_amax = bars + 17;    // [2] all 16 warps have published their dS block maxima of a tile (by tile parity)
-  uint64_t* full = bars + 19;        // [kStages] Q, dO, lse, delta of the stage landed
-  uint64_t* empty = bars + 23;       // [kStages]
-  uint64_t* bar_fin = bars + 27;     // every chain of the CTA is done
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 28);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 29);
-  static_assert(30 * 8 <= 256, "barrier block");
-
-  const int tid = threadIdx.x, warp = tid >> 5;
-  const int n_t = p.N / 128;
-  const int kt = blockIdx.x;                          // causal: tile 0 has the most query tiles and starts first
-  const int bhk = blockIdx.y;
-  const int b = bhk / p.Hk, hk = bhk % p.Hk;
-  const int rep = p.H / p.Hk;
-  const int qt0 = p.causal ? kt : 0;
-  const int n_qi = n_t - qt0;
-  const int n_it = rep * n_qi;                        // iteration = (query head of the group, query tile)
-
-  if (tid == 0) {
-    mbar_init(bar_kv, 1);
-    mbar_init(bar_fin, 1);
-    for (int t = 0; t < 2; ++t) {
-      mbar_init(bar_s + t, 1);
-      mbar_init(bar_dp + t, 1);
-      mbar_init(bar_dv + t, 1);
-      mbar_init(bar_dk + t, 1);
-      mbar_init(bar_sfree + t, kW / 2);
-      mbar_init(bar_dpfree + t, kW / 2);
-      mbar_init(bar_pv + t, kW / 2);
-      mbar_init(bar_pk + t, kW / 2);
-      mbar_init(bar_amax + t, kW);
-    }
-    for (int s = 0; s < C::kStages; ++s) {
-      mbar_init(full + s, 1);
-      mbar_init(empty + s, 1);
-    }
-    *abort_flag = 0;
-    mbar_fence_init();
-  }
-  if (warp == kW + 1) {
-    tmem_alloc(tmem_slot, C::kTmemCols);
-    tmem_relinquish();
-    tc_fence_before();
-  }
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem = *tmem_slot;
-
-  if (warp == kW) {
-    // ------------------------------------------------------------------------------------------ TMA producer
-    if (elect_one()) {
-      tma_prefetch_desc(&tm_q);
-      tma_prefetch_desc(&tm_k);
-      tma_prefetch_desc(&tm_v);
-      tma_prefetch_desc(&tm_do);
-      mbar_expect_tx(bar_kv, 2 * C::kTileBytes);
-      tma_load_2d(sK, &tm_k, bar_kv, 0, bhk * p.N + kt * 128);
-      tma_load_2d(sV, &tm_v, bar_kv, 0, bhk * p.N + kt * 128);
-      int h = hk * rep, qi = 0;
-      for (int it = 0; it < n_it; ++it) {
-        const int st = it % C::kStages;
-        if (it >= C::kStages) {
-          if (!wait_or_abort(empty + st, ((it / C::kStages) - 1) & 1, abort_flag)) {
-            raise_abort(abort_flag, p.status, kStatusTimeoutProducer);
-            break;
-          }
-        }
-        const size_t row = static_cast<size_t>(b * p.H + h) * p.N + (qt0 + qi) * 128;
-        mbar_expect_tx(full + st, 2 * C::kTileBytes + 1024);
-        tma_load_2d(sQ + st * C::kTileBytes, &tm_q, full + st, 0, static_cast<int>(row));
-        tma_load_2d(sDo + st * C::kTileBytes, &tm_do, full + st, 0, static_cast<int>(row));
-        bulk_load_1d(sVec + st * 256, p.lse + row, 512, full + st);
-        bulk_load_1d(sVec + st * 256 + 128, p.delta + row, 512, full + st);
-        if (++qi == n_qi) {
-          qi = 0;
-          ++h;
-        }
-      }
-    }
-  } else if (warp == kW + 1) {
-    // ------------------------------------------------------------------------------------------ MMA issuer
-    if (elect_one()) {
-      constexpr uint32_t kIdesc64 = idesc_f8(128, 64, false, false);
-      constexpr uint32_t kIdescBs = idesc_mxf8(128, 128, false, true, 0, 0);
-      const uint32_t k_lo = desc_lo(smem_u32(sK)), v_lo = desc_lo(smem_u32(sV));
-      const uint32_t q_lo0 = desc_lo(smem_u32(sQ)), do_lo0 = desc_lo(smem_u32(sDo));
-      const bool ws = p.ds_codes != nullptr;
-      bool ok = true;
-      auto wait = [&](uint64_t* bar, uint32_t parity) -> bool {
-        if (ok) {
-          ok = wait_or_abort(bar, parity, abort_flag);
-          if (ok) tc_fence_after();
-        }
-        return ok;
-      };
-      // S^T of team t's half of tile i: keys x the team's 64 queries (rows 64 t ... of the Q tile) into the team's region
-      auto issue_s = [&](int t, int i) {
-        const int st = i % C::kStages;
-        if (!wait(full + st, (i / C::kStages) & 1)) return;
-        const uint32_t q_lo = q_lo0 + st * (C::kTileBytes >> 4) + t * 512;
-#pragma unroll
-        for (int ks = 0; ks < 4; ++ks) mma_f8_ss(tmem + C::kColSd + 64 * t, k_lo + ks * 2, q_lo + ks * 2, kIdesc64, ks > 0);
-        tc_commit(bar_s + t);
-      };
-      auto issue_dp = [&](int t, int i) {
-        const uint32_t do_lo = do_lo0 + (i % C::kStages) * (C::kTileBytes >> 4) + t * 512;
-#pragma unroll
-        for (int ks = 0; ks < 4; ++ks) mma_f8_ss(tmem + C::kColSd + 64 * t, v_lo + ks * 2, do_lo + ks * 2, kIdesc64, ks > 0);
-        tc_commit(bar_dp + t);
-      };
-      // dV += P^T dO over the team's 64 queries: A = P^T codes in TMEM (8 columns per 32-query step), B = dO rows MN-major
-      auto issue_dv = [&](int t, int i) {
-        const uint32_t do_lo = do_lo0 + (i % C::kStages) * (C::kTileBytes >> 4);
-#pragma unroll
-        for (int s = 0; s < 2; ++s) {
-          const int ks = 2 * t + s;
-          mma_mxf8_ts(tmem + C::kColDv, tmem + C::kColPc + ks * 8, do_lo + ks * 256, kIdescBs, tmem + C::kColXv + 4 * ks,
-                      tmem + C::kColOne, (i > 0) || (ks > 0));
-        }
-        tc_commit(bar_dv + t);
-      };
-      auto issue_dk = [&](int t, int j) {
-        const uint32_t q_lo = q_lo0 + (j % C::kStages) * (C::kTileBytes >> 4);
-#pragma unroll
-        for (int s = 0; s < 2; ++s) {
-          const int ks = 2 * t + s;
-          mma_mxf8_ts(tmem + C::kColDk, tmem + C::kColDc + ks * 8, q_lo + ks * 256, kIdescBs, tmem + C::kColXk + 4 * ks,
-                      tmem + C::kColOne, (j > 0) || (ks > 0));
-        }
-      };
-      wait(bar_kv, 0);
-      if (ok) issue_s(0, 0);
-      // Period i of the program: dP_A(i), dK_B(i-2), S_B(i), dV_A(i), dP_B(i), dK_A(i-1), S_A(i+1), dV_B(i).  In the first
-      // period S_B(0) is held back behind dV_A(0), which starts team B half a tile after team A.
-      for (int i = 0; ok && i < n_it + 2; ++i) {
-        const uint32_t ph = i & 1;
-        if (i < n_it && wait(bar_sfree + 0, ph)) issue_dp(0, i);
-        if (i >= 2 && wait(bar_pk + 1, ph)) {
-          const int j = i - 2;
-          issue_dk(1, j);
-          if (ws) {
-            // both halves of the dS^T codes of tile j are in staging tile j & 1: send it to the workspace
-            const int hq_j = hk * rep + j / n_qi, qt_j = qt0 + j % n_qi;
-            const int ws_tile = ((b * p.H + hq_j) * n_t + qt_j) * n_t + kt;
-            tma_store_2d(&tm_ds, sWs + (j & 1) * C::kTileBytes, 0, ws_tile * 128);
-            bulk_commit_group();
-            bulk_wait_group_read<1>();
-          }
-          tc_commit(empty + (j % C::kStages));
-          tc_commit(bar_dk + 1);
-        }
-        if (i > 0 && i < n_it && (wait(bar_dpfree + 1, ph ^ 1))) issue_s(1, i);
-        if (i < n_it && wait(bar_pv + 0, ph)) issue_dv(0, i);
-        if (i == 0 && ok) issue_s(1, 0);
-        if (i < n_it && wait(bar_sfree + 1, ph)) issue_dp(1, i);
-        if (i >= 1 && i <= n_it && wait(bar_pk + 0, ph ^ 1)) {
-          issue_dk(0, i - 1);
-          // the store of tile i - 2 (issued above) has read its staging tile before team A may take this commit as the
-          // permission to overwrite it with tile i
-          if (ws) bulk_wait_group_read<0>();
-          tc_commit(bar_dk + 0);
-        }
-        if (i + 1 < n_it && wait(bar_dpfree + 0, ph)) issue_s(0, i + 1);
-        if (i < n_it && wait(bar_pv + 1, ph)) issue_dv(1, i);
-      }
-      if (ok) tc_commit(bar_fin);
-      if (ws) bulk_wait_group<0>();
-      if (!ok) raise_abort(abort_flag, p.status, kStatusTimeoutMma);
-    }
-  } else {
-    // ------------------------------------------------------------------------------------------ compute teams
-    const int team = warp >> 3;
-    const int wg = warp >> 2;                          // 32-query block of every tile (blocks 2 team, 2 team + 1)
-    const int quad = warp & 3;                         // lane quadrant = 32-key block of the dS scale
-    const int r = tid & 127;                           // key row inside the tile = TMEM lane
-    const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
-    const int key = kt * 128 + r;
-    const int nblk = p.N / 32;
-    const float ks_row = p.ks[static_cast<size_t>(bhk) * nblk + key / 32];
-    const float vs_row = p.vs[static_cast<size_t>(bhk) * nblk + key / 32];
-    const float2 nlog2e = splat2(-kLog2e);
-    const uint32_t vec_a = smem_u32(sVec), xch_a = smem_u32(sXch), ws_a = smem_u32(sWs);
-    const bool ws = p.ds_codes != nullptr;
-    bool ok = true;
-    int st = 0, qi = 0;
-    uint32_t st_ph = 0;
-    // offset of the iteration's scales in p.qs / p.dos (B * H * N / 32 < 2^31)
-    int sc_off = (b * p.H + hk * rep) * nblk + qt0 * 4 + wg;
-    float qs_n = p.qs[sc_off], dos_n = p.dos[sc_off];
-    int hq = hk * rep;                                 // query head of the iteration
-    float2 hd[16];                                     // -dS of the previous tile, waiting for its scale
-    float qs_h = 0.f;                                  // Q scale of the held tile's query block
-    uint32_t ws_tile_h = 0;                            // workspace tile of the held dS (below 2^24 tiles per call)
-
-    // dS codes of tile j from the held values: scale from the maxima of all four query blocks of this quadrant
-    auto convert_held = [&](int j) {
-      const uint32_t pj = j & 1;
-      if (ok) ok = wait_warp(bar_amax + pj, (j >> 1) & 1, abort_flag);
-      // the team's previous dK chain has read the code and word columns (and the workspace store of tile j - 2 its
-      // staging tile)
-      if (ok && j > 0) ok = wait_warp(bar_dk + team, (j - 1) & 1, abort_flag);
-      if (!ok) return;
-      const uint32_t x_a = xch_a + 4 * (pj * 16 + quad);
-      const float am = fmaxf(fmaxf(lds_f(x_a), lds_f(x_a + 16)), fmaxf(lds_f(x_a + 32), lds_f(x_a + 48)));
-      const uint32_t dsb = pow2_sb(am, 127u);
-      uint32_t w[8];
-      codes32(hd, -sb_to_inv(dsb), w);
-      tmem_st8(tmem + lane_base + C::kColDc + 8 * wg, w);
-      const uint32_t xk = sb_mul(dsb, scale_to_sb(qs_h));
-      tmem_st4(tmem + lane_base + C::kColXk + 4 * wg, xk, xk, xk, xk);
-      if (ws) {
-        // the same codes as a [key][query] tile in 128-byte-swizzled shared memory (16-byte chunk c of row r at chunk
-        // c ^ (r % 8)); the MMA warp's thread stores the tile to the workspace for pass 2
-        const uint32_t ws_row = ws_a + pj * C::kTileBytes + r * 128;
-        sts_u4(ws_row + (((2 * wg) ^ (r & 7)) << 4), w[0], w[1], w[2], w[3]);
-        sts_u4(ws_row + (((2 * wg + 1) ^ (r & 7)) << 4), w[4], w[5], w[6], w[7]);
-        fence_async_smem();
-        if (wg == 0 && (tid & 31) == 0) p.ds_words[static_cast<size_t>(ws_tile_h) * 4 + quad] = static_cast<uint8_t>(dsb);
-      }
-      tmem_wait_st();
-      tc_fence_before();
-      __syncwarp();
-      if ((tid & 31) == 0) mbar_arrive(bar_pk + team);
-    };
-
-    if (wg == 0) {                                     // scale 1.0 for every B operand, written once
-      tmem_st4(tmem + lane_base + C::kColOne, 0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu);
-      tmem_wait_st();
-      tc_fence_before();
-    }
-#pragma unroll 1
-    for (int it = 0; ok && it < n_it; ++it) {
-      const uint32_t ph = it & 1;
-      const bool diag = p.causal && (qi == 0);           // the first query tile of a causal sweep is the diagonal one
-      const uint32_t ws_tile = static_cast<uint32_t>(((b * p.H + hq) * n_t + (qt0 + qi)) * n_t + kt);
-      const float qs_c = qs_n, dos_c = dos_n;
-      {                                                  // advance to the next (head, tile) and prefetch its scales
-        sc_off += (qi + 1 == n_qi) ? (nblk - (n_qi - 1) * 4) : 4;
-        if (it + 1 < n_it) {
-          qs_n = p.qs[sc_off];
-          dos_n = p.dos[sc_off];
-        }
-      }
-      const uint32_t lse_a = vec_a + st * 1024 + 128 * wg;         // shared-window addresses of lse / delta of the stage
-      const uint32_t dl_a = lse_a + 512;
-      float2 pr[16];
-      // ---- exponentials: S^T of the team's half -> P, P^T codes
-      ok = wait_warp(full + st, st_ph, abort_flag);                // lse / delta of the tile are in shared memory
-      if (ok) ok = wait_warp(bar_s + team, ph, abort_flag);
-      if (!ok) break;
-      {
-        tc_fence_after();
-        uint32_t rs[32];
-        tmem_ld32(tmem + lane_base + C::kColSd + 32 * wg, rs);
-        tmem_wait_ld();
-        tc_fence_before();
-        __syncwarp();
-        if ((tid & 31) == 0) mbar_arrive(bar_sfree + team);
-        if (diag) {
-#pragma unroll
-          for (int e = 0; e < 32; ++e)
-            if (r > 32 * wg + e) rs[e] = 0xff800000u;              // -inf: key index above the query index
-        }
-        const float2 cc = splat2((ks_row * qs_c) * kLog2e);
-        float pm0 = 0.f, pm1 = 0.f;
-#pragma unroll
-        for (int e = 0; e < 16; e += 2) {
-          const float4 l4 = lds_f4(lse_a + 4 * (2 * e));
-          const float2 x0 = fma2(make_float2(__uint_as_float(rs[2 * e]), __uint_as_float(rs[2 * e + 1])), cc,
-                                 mul2(make_float2(l4.x, l4.y), nlog2e));
-          const float2 x1 = fma2(make_float2(__uint_as_float(rs[2 * e + 2]), __uint_as_float(rs[2 * e + 3])), cc,
-                                 mul2(make_float2(l4.z, l4.w), nlog2e));
-          pr[e] = ex2_2(x0);
-          pr[e + 1] = ex2_2(x1);
-          pm0 = max3(pm0, pr[e].x, pr[e].y);
-          pm1 = max3(pm1, pr[e + 1].x, pr[e + 1].y);
-        }
-        // P^T codes: one power-of-two scale per (key row, 32 queries) = per thread and tile
-        const uint32_t psb = pow2_sb(fmaxf(pm0, pm1), 0u);
-        uint32_t w[8];
-        codes32(pr, sb_to_inv(psb), w);
-        const uint32_t xv = sb_mul(psb, scale_to_sb(dos_c));
-        if (it > 0) ok = wait_warp(bar_dv + team, ph ^ 1, abort_flag);   // the previous dV chain has read codes and words
-        if (!ok) break;
-        tmem_st8(tmem + lane_base + C::kColPc + 8 * wg, w);
-        tmem_st4(tmem + lane_base + C::kColXv + 4 * wg, xv, xv, xv, xv);
-        tmem_wait_st();
-        tc_fence_before();
-        __syncwarp();
-        if ((tid & 31) == 0) mbar_arrive(bar_pv + team);
-      }
-      // ---- the held dS of the previous tile: every maximum of that tile has been published by now
-      if (it > 0) convert_held(it - 1);
-      // ---- dS of this tile from dP^T (its chain was issued when S^T was handed back)
-      if (ok) ok = wait_warp(bar_dp + team, ph, abort_flag);
-      if (!ok) break;
-      {
-        tc_fence_after();
-        uint32_t rd[32];
-        tmem_ld32(tmem + lane_base + C::kColSd + 32 * wg, rd);
-        tmem_wait_ld();
-        tc_fence_before();
-        __syncwarp();
-        if ((tid & 31) == 0) mbar_arrive(bar_dpfree + team);
-        // -dS = P (delta - dP_acc a): a is a power of two, so the product is exact; the sign is undone by the scale
-        const float2 naa = splat2(-(vs_row * dos_c));
-        float am0 = 0.f, am1 = 0.f;
-#pragma unroll
-        for (int e = 0; e < 16; e += 2) {
-          const float4 d4 = lds_f4(dl_a + 4 * (2 * e));
-          const float2 t0 = fma2(make_float2(__uint_as_float(rd[2 * e]), __uint_as_float(rd[2 * e + 1])), naa,
-                                 make_float2(d4.x, d4.y));
-          const float2 t1 = fma2(make_float2(__uint_as_float(rd[2 * e + 2]), __uint_as_float(rd[2 * e + 3])), naa,
-                                 make_float2(d4.z, d4.w));
-          hd[e] = mul2(pr[e], t0);
-          hd[e + 1] = mul2(pr[e + 1], t1);
-          am0 = max3(am0, fabsf(hd[e].x), fabsf(hd[e].y));
-          am1 = max3(am1, fabsf(hd[e + 1].x), fabsf(hd[e + 1].y));
-        }
-        const float wm = warp_max(fmaxf(am0, am1));
-        if ((tid & 31) == 0) {
-          sts_f(xch_a + 4 * (ph * 16 + warp), wm);
-          mbar_arrive(bar_amax + ph);
-        }
-        qs_h = qs_c;
-        ws_tile_h = ws_tile;
-      }
-      if (++st == C::kStages) {
-        st = 0;
-        st_ph ^= 1;
-      }
-      if (++qi == n_qi) {
-        qi = 0;
-        ++hq;
-      }
-    }
-    if (ok) convert_held(n_it - 1);
-    if (ok) ok = wait_warp(bar_fin, 0, abort_flag);
-    if (!ok) {
-      raise_abort(abort_flag, p.status, kStatusTimeoutCompute);
-    } else {
-      tc_fence_after();
-      uint32_t rr[32];
-      tmem_ld32(tmem + lane_base + C::kColDv + 32 * wg, rr);
-      tmem_wait_ld();
-      store_bf16_chunk(rr, 1.0f, p.dv + static_cast<int64_t>(b) * p.dv_sb + static_cast<int64_t>(key) * p.dv_sn +
-                                     static_cast<int64_t>(hk) * p.dv_sh + 32 * wg);
-      tmem_ld32(tmem + lane_base + C::kColDk + 32 * wg, rr);
-      tmem_wait_ld();
-      store_bf16_chunk(rr, 1.0f, p.dk + static_cast<int64_t>(b) * p.dk_sb + static_cast<int64_t>(key) * p.dk_sn +
-                                     static_cast<int64_t>(hk) * p.dk_sh + 32 * wg);
-    }
-  }
-  tc_fence_before();
-  __syncthreads();
-  if (warp == kW + 1) tmem_dealloc(tmem, C::kTmemCols);
-}
-
 // ================================================================================================ dQ
 template <int D>
 struct DqSerialCfg {
@@ -1775,36 +1352,12 @@ cudaError_t launch_bwd_dkdv(int D, const CUtensorMap& tq, const CUtensorMap& tk,
                             cudaStream_t stream) {
   const CUtensorMap* tds = (tds_or_null != nullptr) ? tds_or_null : &tq;     // unused by the kernel without a workspace
   if (D == 128) {
-    // DM_KV_GROUPS (tuning): compute groups of the pipelined kernel, 4 (32 query columns per thread; default, 1.26 ms at
-    // B=4 N=4096 H=32 Hk=8 on B200) or 2 (64 columns per thread, 1.30 ms)
-    static const int groups = [] {
-      const char* e = getenv("DM_KV_GROUPS");
-      return (e != nullptr && e[0] == '2') ? 2 : 4;
-    }();
     dim3 grid(p.N / 128, p.B * p.Hk);
-    static const bool use_pipe = [] {
-      const char* e = getenv("DM_KV_KERNEL");
-      return e != nullptr && e[0] == 'p';
-    }();
-    if (!use_pipe) {
-      static bool done[64] = {};
-      cudaError_t e = set_smem(bwd_dkdv_team_kernel, KvTeamCfg::kSmemBytes, done);
-      if (e != cudaSuccess) return e;
-      bwd_dkdv_team_kernel<<<grid, KvTeamCfg::kThreads, KvTeamCfg::kSmemBytes, stream>>>(tq, tk, tv, tdo, *tds, p);
-      count_launch();
-      return cudaGetLastError();
-    }
-    if (groups == 4) {
-      static bool done[64] = {};
-      cudaError_t e = set_smem(bwd_dkdv_pipe_kernel<4>, KvPipeCfg<4>::kSmemBytes, done);
-      if (e != cudaSuccess) return e;
-      bwd_dkdv_pipe_kernel<4><<<grid, KvPipeCfg<4>::kThreads, KvPipeCfg<4>::kSmemBytes, stream>>>(tq, tk, tv, tdo, *tds, p);
-    } else {
-      static bool done[64] = {};
-      cudaError_t e = set_smem(bwd_dkdv_pipe_kernel<2>, KvPipeCfg<2>::kSmemBytes, done);
-      if (e != cudaSuccess) return e;
-      bwd_dkdv_pipe_kernel<2><<<grid, KvPipeCfg<2>::kThreads, KvPipeCfg<2>::kSmemBytes, stream>>>(tq, tk, tv, tdo, *tds, p);
-    }
+    static bool done[64] = {};
+    cudaError_t e = set_smem(bwd_dkdv_pipe_kernel<4>, KvPipeCfg<4>::kSmemBytes, done);
+    if (e != cudaSuccess) return e;
+    bwd_dkdv_pipe_kernel<4><<<grid, KvPipeCfg<4>::kThreads, KvPipeCfg<4>::kSmemBytes, stream>>>(tq, tk, tv, tdo, *tds, p);
+    count_launch();
     return cudaGetLastError();
   }
   // head_dim 256: S^T + dP^T + dK + dV exceed the 512 TMEM columns, so dV and dK run as two launches

@@ -69,6 +69,9 @@ __device__ __forceinline__ uint64_t global_ns() {
 // early when another role of the CTA has already raised the abort flag.  Returns false on give-up; the caller records a
 // status code, raises the flag and leaves its loop.
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
+#ifndef DM_POLL_NS
+#define DM_POLL_NS 40        // sleep between two polls of a phase that is not complete yet
+#endif
 __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
                                               uint64_t limit_ns = kWaitLimitNs) {
   if (mbar_test_wait(bar, parity)) return true;      // the common case in a pipeline that runs ahead: already complete
@@ -83,7 +86,7 @@ __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, vo
   const uint32_t check_mask = (limit_ns < 100000000ull) ? 0u : 255u;
 #pragma unroll 1
   for (uint32_t spins = 1;; ++spins) {
-    __nanosleep(40);
+    __nanosleep(DM_POLL_NS);
     if (mbar_try_wait(bar, parity)) return true;
     if ((spins & check_mask) == 0u) {
       if (*abort_flag != 0) return false;

@@ -12,7 +12,6 @@
 //
 // Work item = one 128-query tile of one (batch, query head); a CTA walks a list of items.  Warps 0-3: softmax / epilogue
 // (thread t owns TMEM lane t = query row t).  Warp 4: TMA producer.  Warp 5: MMA issuer and TMEM owner.  Every mbarrier wait is bounded.
-#include <cstdlib>
 #include <type_traits>
 #include <cuda_bf16.h>
 #include "dm_common.cuh"
@@ -349,358 +348,6 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
   if (warp == 5) tmem_dealloc(tmem, C::kTmemCols);
 }
 
-// ================================================================================================ two warps per row
-// The same forward with eight softmax warps per CTA: warps w and w + 4 share the 32 query rows of TMEM lane quadrant
-// w % 4 and split the 128 key columns of a tile (warp w: key blocks 0, 1; warp w + 4: blocks 2, 3), which halves the
-// dependent chain of a row per tile and puts four softmax warps on every scheduler (two CTAs per SM).  P codes of a
-// block depend on that block alone, so both warps write their codes at once, each into S columns of its own half
-// (blocks 0, 1 -> columns 0-15, blocks 2, 3 -> columns 64-79); the second warp then hands its block maxima, exponents
-// and sums to the first through shared memory, and the first warp, which owns the row's running maximum and sum,
-// writes the scale words.  Every sum is taken in the order of the one-warp kernel: O and LSE are bit-identical to it.
-template <int D>
-struct Fwd2Cfg {
-  static constexpr int kSub = D / 128;
-  static constexpr int kTileBytes = 128 * D;
-  static constexpr int kStages = 2;
-  static constexpr int kThreads = 8 * 32 + 64;
-  static constexpr int kTmemCols = (D == 128) ? 256 : 512;
-  static constexpr int kColS = 0;                      // S accumulator; P codes of blocks 0, 1 reuse columns 0-15
-  static constexpr int kColPhi = 64;                   // P codes of blocks 2, 3 reuse columns 64-79
-  static constexpr int kColSfa = 32;
-  static constexpr int kColSfb = 36;
-  static constexpr int kColO = 128;
-  static constexpr int kSmemQ = 0;
-  static constexpr int kSmemK = kTileBytes;
-  static constexpr int kSmemV = kSmemK + kStages * kTileBytes;
-  static constexpr int kSmemOut = kSmemV + kStages * kTileBytes;   // 8 warps x 32 rows x 80 bytes: O write-out staging
-  static constexpr int kOutRow = 80;
-  static constexpr int kSmemXch = kSmemOut + 8 * 32 * kOutRow;     // 2 x 128 rows x 8 floats: second warp -> first warp
-  static constexpr int kSmemBar = kSmemXch + 2 * 128 * 32;
-  static constexpr int kSmemBytes = kSmemBar + 256 + 1024;
-};
-
-template <int D, bool kOrdered>
-__global__ void __launch_bounds__(Fwd2Cfg<D>::kThreads, (D == 128) ? 2 : 1)
-fwd2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-            const __grid_constant__ CUtensorMap tm_v, const FwdParams p) {
-  using C = Fwd2Cfg<D>;
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* sQ = smem + C::kSmemQ;
-  uint8_t* sK = smem + C::kSmemK;
-  uint8_t* sV = smem + C::kSmemV;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kSmemBar);
-  uint64_t* bar_q = bars + 0;
-  uint64_t* bar_s = bars + 1;     // S accumulator ready (MMA commit)
-  uint64_t* bar_p = bars + 2;     // P codes + scale words written (one arrival per softmax warp)
-  uint64_t* bar_o = bars + 3;     // PV chain done (MMA commit)
-  uint64_t* full_k = bars + 4;    // [kStages]
-  uint64_t* full_v = bars + 6;    // [kStages]
-  uint64_t* empty = bars + 8;     // [kStages] stage free again (MMA commit)
-  uint64_t* bar_qfree = bars + 10; // the item's last S chain has read Q (MMA commit)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 13);
-
-  const int tid = threadIdx.x;
-  const int warp = tid >> 5;
-  const int n_qt = p.N / 128;
-  const int BH = p.B * p.H;
-  const int n_items = n_qt * BH;
-  const int rep = p.H / p.Hk;
-  const int first_item = static_cast<int>(blockIdx.x), item_step = static_cast<int>(gridDim.x);
-
-  if (tid == 0) {
-    mbar_init(bar_q, 1);
-    mbar_init(bar_s, 1);
-    mbar_init(bar_p, 8);
-    mbar_init(bar_o, 1);
-    mbar_init(bar_qfree, 1);
-    for (int s = 0; s < C::kStages; ++s) {
-      mbar_init(full_k + s, 1);
-      mbar_init(full_v + s, 1);
-      mbar_init(empty + s, 1);
-    }
-    *abort_flag = 0;
-    mbar_fence_init();
-  }
-  if (warp == 9) {
-    tmem_alloc(tmem_slot, C::kTmemCols);
-    tmem_relinquish();
-    tc_fence_before();
-  }
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem = *tmem_slot;
-
-  if (warp == 8) {
-    // ------------------------------------------------------------------------------------------ TMA producer
-    if (elect_one()) {
-      tma_prefetch_desc(&tm_q);
-      tma_prefetch_desc(&tm_k);
-      tma_prefetch_desc(&tm_v);
-      bool ok = true;
-      int gt = 0, ic = 0;                                 // tiles and items issued so far by this CTA
-      for (int k = 0, item; ok && (item = sched_item(k, first_item, item_step)) < n_items; ++k, ++ic) {
-        const int qt = n_qt - 1 - item / BH, bh = item % BH;
-        const int bhk = (bh / p.H) * p.Hk + (bh % p.H) / rep;
-        const int n_it = p.causal ? (qt + 1) : n_qt;
-        const int kt_first = p.causal ? qt : (n_qt - 1);
-        if (ic > 0 && !(ok = wait_or_abort(bar_qfree, (ic - 1) & 1, abort_flag))) break;
-        mbar_expect_tx(bar_q, C::kTileBytes);
-        for (int s = 0; s < C::kSub; ++s) tma_load_2d(sQ + s * 16384, &tm_q, bar_q, s * 128, bh * p.N + qt * 128);
-        for (int it = 0; it < n_it; ++it, ++gt) {
-          const int st = gt % C::kStages;
-          if (gt >= C::kStages && !(ok = wait_or_abort(empty + st, ((gt / C::kStages) - 1) & 1, abort_flag))) break;
-          const int row = bhk * p.N + (kt_first - it) * 128;
-          mbar_expect_tx(full_k + st, C::kTileBytes);
-          for (int s = 0; s < C::kSub; ++s)
-            tma_load_2d(sK + st * C::kTileBytes + s * 16384, &tm_k, full_k + st, s * 128, row);
-          mbar_expect_tx(full_v + st, C::kTileBytes);
-          for (int s = 0; s < C::kSub; ++s)
-            tma_load_2d(sV + st * C::kTileBytes + s * 16384, &tm_v, full_v + st, s * 128, row);
-        }
-      }
-      if (!ok) raise_abort(abort_flag, p.status, kStatusTimeoutProducer);
-    }
-  } else if (warp == 9) {
-    // ------------------------------------------------------------------------------------------ MMA issuer
-    if (elect_one()) {
-      constexpr uint32_t kIdescS = idesc_f8(128, 128, false, false);
-      const uint32_t q_lo = desc_lo(smem_u32(sQ)), k_lo0 = desc_lo(smem_u32(sK)), v_lo0 = desc_lo(smem_u32(sV));
-      bool ok = true;
-      int gt = 0, ic = 0;
-      for (int k = 0, item; ok && (item = sched_item(k, first_item, item_step)) < n_items; ++k, ++ic) {
-        const int qt = n_qt - 1 - item / BH;
-        const int n_it = p.causal ? (qt + 1) : n_qt;
-        if (!(ok = wait_or_abort(bar_q, ic & 1, abort_flag))) break;
-        for (int it = 0; it < n_it; ++it, ++gt) {
-          const int st = gt % C::kStages;
-          const uint32_t ph = (gt / C::kStages) & 1;
-          if (!(ok = wait_or_abort(full_k + st, ph, abort_flag))) break;
-          // the previous PV chain has read its scale words out of the S columns (see fwd_kernel's kOrdered)
-          if (kOrdered && gt > 0 && !(ok = wait_or_abort(bar_o, (gt - 1) & 1, abort_flag))) break;
-          tc_fence_after();
-          const uint32_t k_lo = k_lo0 + st * (C::kTileBytes >> 4), v_lo = v_lo0 + st * (C::kTileBytes >> 4);
-#pragma unroll
-          for (int ks = 0; ks < D / 32; ++ks) {
-            const uint32_t off = (ks / 4) * 1024 + (ks % 4) * 2;      // descriptor units of 16 bytes
-            mma_f8_ss(tmem + C::kColS, q_lo + off, k_lo + off, kIdescS, ks > 0);
-          }
-          tc_commit(bar_s);
-          if (it == n_it - 1) tc_commit(bar_qfree);
-          if (!(ok = wait_or_abort(bar_p, gt & 1, abort_flag))) break;
-          if (!(ok = wait_or_abort(full_v + st, ph, abort_flag))) break;
-          tc_fence_after();
-          // O += P V: A = P codes in TMEM (8 columns per 32-key step; steps 0, 1 at columns 0-15, steps 2, 3 at 64-79)
-#pragma unroll
-          for (int ks = 0; ks < 4; ++ks) {
-            const uint32_t a_col = (ks < 2) ? (C::kColS + ks * 8) : (C::kColPhi + (ks - 2) * 8);
-#pragma unroll
-            for (int s = 0; s < C::kSub; ++s) {
-              mma_mxf8_ts(tmem + C::kColO + s * 128, tmem + a_col, v_lo + s * 1024 + ks * 256,
-                          idesc_mxf8(128, 128, false, true, ks, ks), tmem + C::kColSfa, tmem + C::kColSfb,
-                          (it > 0) || (ks > 0));
-            }
-          }
-          tc_commit(empty + st);
-          tc_commit(bar_o);
-        }
-      }
-      if (!ok) raise_abort(abort_flag, p.status, kStatusTimeoutMma);
-    }
-  } else {
-    // ------------------------------------------------------------------------------------------ softmax / epilogue
-    const int quad = warp & 3, half = warp >> 2;          // half 0 owns the row's running state
-    const int lane = tid & 31;
-    const int r = quad * 32 + lane;                       // query row inside the tile = TMEM lane
-    const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
-    const int nblk = p.N / 32;
-    float* xch = reinterpret_cast<float*>(smem + C::kSmemXch);
-    bool ok = true;
-    int gt = 0;
-    auto item_qs = [&](int item) -> const float* {
-      const int qt = n_qt - 1 - item / BH, bh = item % BH;
-      return p.qs + static_cast<size_t>(bh) * nblk + (qt * 128 + r) / 32;
-    };
-    // offset, in p.ks / p.vs, of the scales of the first key tile an item visits (B * Hk * N / 32 < 2^31)
-    auto item_kv = [&](int item) -> int {
-      const int qt = n_qt - 1 - item / BH, bh = item % BH;
-      const int bhk = (bh / p.H) * p.Hk + (bh % p.H) / rep;
-      return bhk * nblk + (p.causal ? qt : (n_qt - 1)) * 4;
-    };
-    // the K scales of this warp's two key blocks and the packed V scale bytes of a tile, requested one tile ahead
-    auto load_scales = [&](int off, float2& ks2, uint32_t& sfb) {
-      ks2 = *reinterpret_cast<const float2*>(p.ks + off + 2 * half);
-      const float4 v4 = *reinterpret_cast<const float4*>(p.vs + off);
-      sfb = pack4(scale_to_sb(v4.x), scale_to_sb(v4.y), scale_to_sb(v4.z), scale_to_sb(v4.w));
-    };
-    float qs_next = 0.f;
-    float2 ks_n = make_float2(0.f, 0.f);
-    uint32_t sfb_n = 0;
-    if (first_item < n_items) {
-      qs_next = *item_qs(first_item);
-      load_scales(item_kv(first_item), ks_n, sfb_n);
-    }
-    for (int k = 0, item; (item = sched_item(k, first_item, item_step)) < n_items; ++k) {
-      const int qt = n_qt - 1 - item / BH, bh = item % BH;
-      const int b = bh / p.H, h = bh % p.H;
-      const int n_it = p.causal ? (qt + 1) : n_qt;
-      const float qsl = qs_next * kLog2e;
-      const int item_n = sched_item(k + 1, first_item, item_step);
-      const bool has_next = item_n < n_items;
-      if (has_next) qs_next = *item_qs(item_n);
-      int kv_off = item_kv(item);
-      float m = 0.f, l = 0.f;                             // used by half 0 only
-      auto tile = [&](int it, auto diag_tag) -> bool {
-        constexpr bool kDiag = decltype(diag_tag)::value;
-        const float cb[2] = {qsl * ks_n.x, qsl * ks_n.y};
-        const uint32_t sfb = sfb_n;
-        if (it + 1 < n_it) {
-          kv_off -= 4;
-          load_scales(kv_off, ks_n, sfb_n);
-        } else if (has_next) {
-          load_scales(item_kv(item_n), ks_n, sfb_n);
-        }
-        if (!wait_warp(bar_s, gt & 1, abort_flag)) return false;
-        tc_fence_after();
-        float bsum[2], kb[2], bmax[2];
-        // One 32-column chunk at a time (the scheduler has four softmax warps to cover the load).  The codes of both of
-        // this warp's blocks land inside the columns of its first chunk, which is in registers before the first store.
-#pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          uint32_t rc[32];
-          tmem_ld32(tmem + lane_base + C::kColS + 64 * half + 32 * c, rc);
-          tmem_wait_ld();
-          const int blk = 2 * half + c;
-          if (kDiag) {
-#pragma unroll
-            for (int e = 0; e < 32; ++e)
-              if (32 * blk + e > r) rc[e] = 0xff800000u;       // -inf: key index above the query index
-          }
-          float2 s2[16];
-#pragma unroll
-          for (int e = 0; e < 16; ++e) s2[e] = make_float2(__uint_as_float(rc[2 * e]), __uint_as_float(rc[2 * e + 1]));
-          bmax[c] = max32(s2) * cb[c];
-          kb[c] = fmaxf(floorf(bmax[c]), -1e30f);
-          const float2 c2 = splat2(cb[c]), bias2 = splat2(7.0f - kb[c]);
-          float2 sum0 = make_float2(0.f, 0.f), sum1 = make_float2(0.f, 0.f);
-          uint32_t codes[8];
-#pragma unroll
-          for (int e = 0; e < 16; e += 2) {
-            const float2 p0 = ex2_2(fma2(s2[e], c2, bias2));
-            // three of the sixteen pairs take the polynomial, the same pairs as in the one-warp kernel
-            const float2 p1 = (e == 2 || e == 8 || e == 14) ? ex2_poly2(fma2(s2[e + 1], c2, bias2)) : ex2_2(fma2(s2[e + 1], c2, bias2));
-            sum0 = add2(sum0, p0);
-            sum1 = add2(sum1, p1);
-            codes[e / 2] = cvt_e4m3x4(p0.x, p0.y, p1.x, p1.y);
-          }
-          sum0 = add2(sum0, sum1);
-          bsum[c] = sum0.x + sum0.y;
-          tmem_st8(tmem + lane_base + C::kColS + 64 * half + 8 * c, codes);
-        }
-        float* x = xch + ((gt & 1) * 128 + r) * 8;
-        if (half == 1) {
-          // hand the two blocks' maxima, exponents and sums to the warp that owns the row
-          *reinterpret_cast<float4*>(x) = make_float4(bmax[0], bmax[1], kb[0], kb[1]);
-          *reinterpret_cast<float2*>(x + 4) = make_float2(bsum[0], bsum[1]);
-          bar_arrive(1 + quad, 64);
-        } else {
-          bar_sync(1 + quad, 64);
-          const float4 o4 = *reinterpret_cast<const float4*>(x);
-          const float2 o2 = *reinterpret_cast<const float2*>(x + 4);
-          const float bm[4] = {bmax[0], bmax[1], o4.x, o4.y};
-          const float kk[4] = {kb[0], kb[1], o4.z, o4.w};
-          const float bs[4] = {bsum[0], bsum[1], o2.x, o2.y};
-          const float mcand = ceilf(fmaxf(fmaxf(bm[0], bm[1]), fmaxf(bm[2], bm[3])));
-          float acc_scale = 1.0f;
-          if (it == 0) {
-            m = mcand;
-          } else if (mcand > m + 32.0f) {
-            acc_scale = sb_to_scale(static_cast<uint32_t>(max(0, min(__float2int_rn(m - mcand) + 127, 254))));
-            m = mcand;
-          }
-          if (it > 0 && __any_sync(0xffffffffu, acc_scale != 1.0f)) {
-            // rare: the running max moved by more than 32 binades; rescale this quadrant's O rows in place (eight
-            // columns at a time: the path must not cost the common path registers)
-#pragma unroll 1
-            for (int c = 0; c < D / 8; ++c) {
-              uint32_t ro[8];
-              tmem_ld8(tmem + lane_base + C::kColO + 8 * c, ro);
-              tmem_wait_ld();
-#pragma unroll
-              for (int e = 0; e < 8; ++e) ro[e] = __float_as_uint(__uint_as_float(ro[e]) * acc_scale);
-              tmem_st8(tmem + lane_base + C::kColO + 8 * c, ro);
-            }
-          }
-          l *= acc_scale;
-          uint32_t sb[4];
-#pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            const int e = __float2int_rn(kk[c] - 7.0f - m);      // saturates for fully masked blocks
-            sb[c] = static_cast<uint32_t>(max(0, min(max(e, -1000) + 127, 254)));
-            l = fmaf(bs[c], __uint_as_float(sb[c] << 23), l);
-          }
-          const uint32_t sfa = pack4(sb[0], sb[1], sb[2], sb[3]);
-          tmem_st4(tmem + lane_base + C::kColSfa, sfa, sfa, sfa, sfa);
-          tmem_st4(tmem + lane_base + C::kColSfb, sfb, sfb, sfb, sfb);
-        }
-        tmem_wait_st();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar_p);
-        ++gt;
-        return true;
-      };
-      ok = p.causal ? tile(0, std::true_type{}) : tile(0, std::false_type{});
-      for (int it = 1; ok && it < n_it; ++it) ok = tile(it, std::false_type{});
-      if (ok) ok = wait_warp(bar_o, (gt - 1) & 1, abort_flag);
-      if (!ok) break;
-      tc_fence_after();
-      // the row's 1 / l goes from the owning warp to its partner; each of the two writes half of the columns of O
-      float* xl = xch + (((gt - 1) & 1) * 128 + r) * 8 + 6;       // slot of the item's last tile, words 6-7 are free
-      if (half == 0) {
-        *xl = 1.0f / l;
-        bar_arrive(5 + quad, 64);
-      } else {
-        bar_sync(5 + quad, 64);
-      }
-      const float inv_l = (half == 0) ? (1.0f / l) : *xl;
-      const uint32_t stage_a = smem_u32(smem + C::kSmemOut) + warp * (32 * C::kOutRow);
-      const int out_row0 = qt * 128 + quad * 32;                    // first row of this quadrant
-      __nv_bfloat16* obase = p.o + static_cast<int64_t>(b) * p.o_sb + static_cast<int64_t>(h) * p.o_sh + 8 * (lane & 3);
-      constexpr int kChunks = D / 64;                               // 32-column chunks per warp
-#pragma unroll 1
-      for (int cc = 0; cc < kChunks; ++cc) {
-        const int c = half * kChunks + cc;
-        uint32_t ro[32];
-        tmem_ld32(tmem + lane_base + C::kColO + 32 * c, ro);
-        tmem_wait_ld();
-        uint32_t w[16];
-#pragma unroll
-        for (int e = 0; e < 16; ++e) {
-          __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(ro[2 * e]) * inv_l, __uint_as_float(ro[2 * e + 1]) * inv_l);
-          w[e] = *reinterpret_cast<uint32_t*>(&v);
-        }
-        __syncwarp();                                               // the previous chunk has been read out of the stage
-#pragma unroll
-        for (int e = 0; e < 4; ++e) sts_u4(stage_a + lane * C::kOutRow + 16 * e, w[4 * e], w[4 * e + 1], w[4 * e + 2], w[4 * e + 3]);
-        __syncwarp();
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int ri = 8 * i + (lane >> 2);                       // row of the quadrant this lane writes a quarter of
-          const float4 v = lds_f4(stage_a + ri * C::kOutRow + 16 * (lane & 3));
-          *reinterpret_cast<float4*>(obase + static_cast<int64_t>(out_row0 + ri) * p.o_sn + 32 * c) = v;
-        }
-      }
-      if (half == 0) p.lse[static_cast<size_t>(bh) * p.N + qt * 128 + r] = (m + log2f(l)) * kLn2;
-    }
-    if (!ok) raise_abort(abort_flag, p.status, kStatusTimeoutCompute);
-  }
-  tc_fence_before();
-  __syncthreads();
-  if (warp == 9) tmem_dealloc(tmem, C::kTmemCols);
-}
-
 template <int D, bool kOrdered>
 static cudaError_t launch_fwd_t(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FwdParams& p,
                                 cudaStream_t stream) {
@@ -727,39 +374,8 @@ static cudaError_t launch_fwd_t(const CUtensorMap& tq, const CUtensorMap& tk, co
 }
 
 
-template <int D, bool kOrdered>
-static cudaError_t launch_fwd2_t(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FwdParams& p,
-                                 cudaStream_t stream) {
-  using C = Fwd2Cfg<D>;
-  static bool attr_set[64] = {};
-  static int sm_count[64] = {};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(fwd2_kernel<D, kOrdered>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
-    if (e != cudaSuccess) return e;
-    e = cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev);
-    if (e != cudaSuccess) return e;
-    attr_set[dev] = true;
-  }
-  const int sms = (dev >= 0 && dev < 64) ? sm_count[dev] : 148;
-  const int items = (p.N / 128) * p.B * p.H;
-  const int ctas = sms * ((D == 128) ? 2 : 1);
-  fwd2_kernel<D, kOrdered><<<items < ctas ? items : ctas, C::kThreads, C::kSmemBytes, stream>>>(tq, tk, tv, p);
-  count_launch();
-  return cudaGetLastError();
-}
-
 cudaError_t launch_fwd(int D, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FwdParams& p,
                        cudaStream_t stream) {
-  static const bool two_warps = [] {
-    const char* e = getenv("DM_FWD_WARPS");
-    return e != nullptr && e[0] == '8';
-  }();
-  if (two_warps && !p.unordered) {
-    if (D != 128) return launch_fwd2_t<256, true>(tq, tk, tv, p, stream);
-    return launch_fwd2_t<128, true>(tq, tk, tv, p, stream);
-  }
   // One kernel for both head dims: S (128 columns) plus O (head_dim columns) per CTA, two CTAs per SM at head_dim 128.
   if (p.unordered) {
     if (D != 128) return launch_fwd_t<256, false>(tq, tk, tv, p, stream);

@@ -10,12 +10,13 @@ pytestmark = pytest.mark.gpu
 NAMES = ("O", "dQ", "dK", "dV")
 
 
-# Distance of the kernel to the emulation per logit scale s, measured on B200 at the configuration's full size
-# (DM_TEST_RECORD) and gated at about three times the measurement.  At s = 1 the gates are the reference's own
-# (tests/test_sm100.py:61: 3e-4 for O, 5e-3 for the gradients).  From s = 3 on the logits reach hundreds to thousands of
-# log2 units, so one fp32 rounding of S * c moves P by up to 2^-24 * |x|: the distance grows with s for a kernel that
-# evaluates fma(S, c, bias) in one rounding while the emulation multiplies and subtracts in two.
-SWEEP_GATES = {1.0: dict(O=3e-4, g=5e-3), 3.0: dict(O=6e-4, g=6e-3), 10.0: dict(O=2e-3, g=1e-2), 30.0: dict(O=1e-2, g=2e-2)}
+# Distance of the kernel to the emulation per logit scale s: measured on B200 at the configuration's full size (recorded
+# with DM_TEST_RECORD, maximum over the two emulated batches) and gated at about three times the measurement, never
+# tighter than the reference's own gates (tests/test_sm100.py:61: 3e-4 for O, 5e-3 for the gradients).  Measured O:
+# 1.3e-4 / 5.1e-4 / 1.4e-3 / 3.0e-3 at s = 1 / 3 / 10 / 30; gradients 1.7e-3 / 1.7e-3 / 2.0e-3 / 2.5e-3.  The growth
+# with s is fp32 rounding of the exponent: the logits reach hundreds to thousands of log2 units, and one rounding of
+# fma(S, c, bias) against the emulation's separate multiply and subtract moves P by up to 2^-24 |x|.
+SWEEP_GATES = {1.0: dict(O=3e-4, g=5e-3), 3.0: dict(O=1.5e-3, g=5e-3), 10.0: dict(O=4e-3, g=6e-3), 30.0: dict(O=9e-3, g=7.5e-3)}
 
 
 @pytest.mark.parametrize("s", [1.0, 3.0, 10.0, 30.0])
