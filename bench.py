@@ -49,9 +49,11 @@ WORKLOADS = {
 FP8_NOMINAL_TFLOPS = 4500.0
 SEED = 1234
 # DRAM bytes (read + written) per live 128 x 128 tile position of the dK/dV kernel: one ncu capture of one launch on
-# c2_small (dram__bytes_read.sum + dram__bytes_write.sum over 8448 tile positions; the summary is in profiles/), scaled
-# to a launch by its tile count.  The written part is the dS tile for pass 2 (16 KiB per position).
-DKDV_DRAM_BYTES_PER_TILE = None
+# c2_small (dram__bytes_read.sum 21.79 MB + dram__bytes_write.sum 89.94 MB over 8448 tile positions; the summary is in
+# profiles/), scaled to a launch by its tile count (traffic grows with the tile count: per position one 16 KiB dS tile
+# is written for pass 2, of which about a third was still in L2 when the captured kernel ended, and the Q / dO / K / V
+# tiles are read mostly from L2).
+DKDV_DRAM_BYTES_PER_TILE = 13225.0
 
 
 def counted_flops(B, N, H, D, causal=True):

@@ -17,6 +17,11 @@ from . import torch_ops as _torch_ops  # noqa: F401  (registers torch.ops.delta_
 _OPS = torch.ops.delta_matching_b200
 
 
+def _calls():
+    """The registered ops while a compiler is tracing (it records them as opaque nodes), the plain functions otherwise."""
+    return _OPS if torch.compiler.is_compiling() else _torch_ops.DIRECT
+
+
 def blocks(D: int):
     """Tokens per quantisation scale as (Q / dO rows, K / V keys): one power-of-two scale per 32 tokens over all of
     head_dim at both head dims (the reference's Blackwell contract, delta_matching/sm100/quant.py:1-12; its Hopper
@@ -78,13 +83,14 @@ def _is_sm100(index: int) -> bool:
 
 class _DMAttn(torch.autograd.Function):
     """Forward and backward as calls of the registered ops (delta_matching_b200/torch_ops.py), the way the reference's
-    autograd function calls torch.ops.delta_matching (delta_matching/attn.py:37-118): eager calls run the kernels
-    directly, and a tracing compiler records five opaque ops instead of breaking its graph here."""
+    autograd function calls torch.ops.delta_matching (delta_matching/attn.py:37-118): a tracing compiler records five
+    opaque ops instead of breaking its graph here; eager calls skip the dispatcher and run the same functions directly."""
 
     @staticmethod
     def forward(ctx, q, k, v, causal, delta_mode):
-        q8, qs, k8, ks, v8, vs, _ = _OPS.quant_qkv(q, k, v)
-        o, lse = _OPS.fwd_fp8(q8, k8, v8, qs, ks, vs, causal)
+        K = _calls()
+        q8, qs, k8, ks, v8, vs, _ = K.quant_qkv(q, k, v)
+        o, lse = K.fwd_fp8(q8, k8, v8, qs, ks, vs, causal)
         ctx.save_for_backward(q8, qs, k8, ks, v8, vs, o, lse)
         ctx.causal = causal
         ctx.delta_mode = delta_mode
@@ -94,15 +100,16 @@ class _DMAttn(torch.autograd.Function):
     @torch.autograd.function.once_differentiable
     def backward(ctx, dO):
         q8, qs, k8, ks, v8, vs, o, lse = ctx.saved_tensors
+        K = _calls()
         if dO.stride(-1) != 1:          # e.g. the expanded gradient of o.sum()
             dO = dO.contiguous()
         do_bhnd = dO.permute(0, 2, 1, 3)                   # (B, N, H, D) -> (B, H, N, D) view, read in place
         if ctx.delta_mode == "matched":
-            do8, dos, _ = _OPS.quant_do(do_bhnd, do_bhnd, False)       # the matched mode never reads O
-            delta = _OPS.delta_fp8(q8, k8, v8, do8, qs, ks, vs, dos, lse, ctx.causal)
+            do8, dos, _ = K.quant_do(do_bhnd, do_bhnd, False)       # the matched mode never reads O
+            delta = K.delta_fp8(q8, k8, v8, do8, qs, ks, vs, dos, lse, ctx.causal)
         else:
-            do8, dos, delta = _OPS.quant_do(do_bhnd, o.permute(0, 2, 1, 3), True)
-        dq, dk, dv = _OPS.bwd_fp8(q8, k8, v8, do8, qs, ks, vs, dos, lse, delta, ctx.causal)
+            do8, dos, delta = K.quant_do(do_bhnd, o.permute(0, 2, 1, 3), True)
+        dq, dk, dv = K.bwd_fp8(q8, k8, v8, do8, qs, ks, vs, dos, lse, delta, ctx.causal)
         return dq.permute(0, 2, 1, 3), dk.permute(0, 2, 1, 3), dv.permute(0, 2, 1, 3), None, None
 
 

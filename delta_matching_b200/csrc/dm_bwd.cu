@@ -22,10 +22,10 @@
 
 namespace dm {
 
+// Maximum over the warp of a non-negative value: non-negative floats order like their bit patterns, so one integer
+// redux.sync does the work of a five-step shuffle butterfly.
 __device__ __forceinline__ float warp_max(float v) {
-#pragma unroll
-  for (int off = 16; off > 0; off >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, off));
-  return v;
+  return __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(v)));
 }
 
 // Row of an fp32 TMEM accumulator (32-column chunk c) -> bf16, 64 bytes to global.

@@ -29,9 +29,11 @@ F32 = torch.float32
 BF16 = torch.bfloat16
 
 
-@torch.library.custom_op(f"{NS}::quant_qkv", mutates_args=(), device_types="cuda")
-def quant_qkv(q: Tensor, k: Tensor, v: Tensor) -> Tuple[Tensor, Tensor, Tensor, Tensor, Tensor, Tensor, Tensor]:
+def _quant_qkv(q: Tensor, k: Tensor, v: Tensor) -> Tuple[Tensor, Tensor, Tensor, Tensor, Tensor, Tensor, Tensor]:
     return ops.quant_qkv(q, k, v)
+
+
+quant_qkv = torch.library.custom_op(f"{NS}::quant_qkv", _quant_qkv, mutates_args=(), device_types="cuda")
 
 
 @quant_qkv.register_fake
@@ -43,9 +45,11 @@ def _(q, k, v):
     return code(H), scale(H), code(Hk), scale(Hk), code(Hk), scale(Hk), q.new_empty((B, Hk, D), dtype=F32)
 
 
-@torch.library.custom_op(f"{NS}::fwd_fp8", mutates_args=(), device_types="cuda")
-def fwd_fp8(q8: Tensor, k8: Tensor, v8: Tensor, qs: Tensor, ks: Tensor, vs: Tensor, causal: bool) -> Tuple[Tensor, Tensor]:
+def _fwd_fp8(q8: Tensor, k8: Tensor, v8: Tensor, qs: Tensor, ks: Tensor, vs: Tensor, causal: bool) -> Tuple[Tensor, Tensor]:
     return ops.fwd_fp8(q8, k8, v8, qs, ks, vs, causal)
+
+
+fwd_fp8 = torch.library.custom_op(f"{NS}::fwd_fp8", _fwd_fp8, mutates_args=(), device_types="cuda")
 
 
 @fwd_fp8.register_fake
@@ -54,13 +58,15 @@ def _(q8, k8, v8, qs, ks, vs, causal):
     return q8.new_empty((B, N, H, D), dtype=BF16), q8.new_empty((B, H, N), dtype=F32)
 
 
-@torch.library.custom_op(f"{NS}::quant_do", mutates_args=(), device_types="cuda")
-def quant_do(do: Tensor, o: Tensor, with_o: bool) -> Tuple[Tensor, Tensor, Tensor]:
+def _quant_do(do: Tensor, o: Tensor, with_o: bool) -> Tuple[Tensor, Tensor, Tensor]:
     """with_o: also return the stale delta rowsum(dO * O); otherwise `o` is not read and delta comes back empty."""
     do8, dos, delta = ops.quant_do(do, o if with_o else None)
     if delta is None:
         delta = do.new_empty((0,), dtype=F32)
     return do8, dos, delta
+
+
+quant_do = torch.library.custom_op(f"{NS}::quant_do", _quant_do, mutates_args=(), device_types="cuda")
 
 
 @quant_do.register_fake
@@ -70,10 +76,12 @@ def _(do, o, with_o):
     return do.new_empty((B, H, N, D), dtype=E4M3), do.new_empty((B, H, N // ops.BLK), dtype=F32), delta
 
 
-@torch.library.custom_op(f"{NS}::delta_fp8", mutates_args=(), device_types="cuda")
-def delta_fp8(q8: Tensor, k8: Tensor, v8: Tensor, do8: Tensor, qs: Tensor, ks: Tensor, vs: Tensor, dos: Tensor,
-              lse: Tensor, causal: bool) -> Tensor:
+def _delta_fp8(q8: Tensor, k8: Tensor, v8: Tensor, do8: Tensor, qs: Tensor, ks: Tensor, vs: Tensor, dos: Tensor,
+               lse: Tensor, causal: bool) -> Tensor:
     return ops.delta_fp8(q8, k8, v8, do8, qs, ks, vs, dos, lse, causal)
+
+
+delta_fp8 = torch.library.custom_op(f"{NS}::delta_fp8", _delta_fp8, mutates_args=(), device_types="cuda")
 
 
 @delta_fp8.register_fake
@@ -81,10 +89,12 @@ def _(q8, k8, v8, do8, qs, ks, vs, dos, lse, causal):
     return torch.empty_like(lse)
 
 
-@torch.library.custom_op(f"{NS}::bwd_fp8", mutates_args=(), device_types="cuda")
-def bwd_fp8(q8: Tensor, k8: Tensor, v8: Tensor, do8: Tensor, qs: Tensor, ks: Tensor, vs: Tensor, dos: Tensor,
-            lse: Tensor, delta: Tensor, causal: bool) -> Tuple[Tensor, Tensor, Tensor]:
+def _bwd_fp8(q8: Tensor, k8: Tensor, v8: Tensor, do8: Tensor, qs: Tensor, ks: Tensor, vs: Tensor, dos: Tensor,
+             lse: Tensor, delta: Tensor, causal: bool) -> Tuple[Tensor, Tensor, Tensor]:
     return ops.bwd_fp8(q8, k8, v8, do8, qs, ks, vs, dos, lse, delta, causal)
+
+
+bwd_fp8 = torch.library.custom_op(f"{NS}::bwd_fp8", _bwd_fp8, mutates_args=(), device_types="cuda")
 
 
 @bwd_fp8.register_fake
@@ -93,3 +103,16 @@ def _(q8, k8, v8, do8, qs, ks, vs, dos, lse, delta, causal):
     Hk = k8.shape[1]
     return (q8.new_empty((B, N, H, D), dtype=BF16), q8.new_empty((B, N, Hk, D), dtype=BF16),
             q8.new_empty((B, N, Hk, D), dtype=BF16))
+
+
+class _Direct:
+    """The same five calls without the dispatcher in between: what the eager path uses (a registered op costs tens of
+    microseconds of host time per call, which shows once the kernels of a step take about two milliseconds)."""
+    quant_qkv = staticmethod(_quant_qkv)
+    fwd_fp8 = staticmethod(_fwd_fp8)
+    quant_do = staticmethod(_quant_do)
+    delta_fp8 = staticmethod(_delta_fp8)
+    bwd_fp8 = staticmethod(_bwd_fp8)
+
+
+DIRECT = _Direct
