@@ -451,6 +451,24 @@ def e2e_leg(job, steps, barrier, allmax):
                   "chunks pipelined over three streams)"}
     if job.input_bytes() <= (2 << 30):
         dev_in = [torch.empty_like(x) for x in (job.q, job.k, job.v, job.do)]
+        dev_out = [torch.empty_like(x) for x in (job.q, job.q, job.k, job.v)]
+        side = torch.cuda.Stream()
+
+        def copies_only():
+            # the step's PCIe traffic alone: inputs in on one stream while the outputs of the previous step go out on
+            # another (dense copies, no kernels): the floor of the end-to-end figure on this host
+            side.wait_stream(stream)
+            with torch.cuda.stream(side):
+                for h_, d_ in zip(host_out, dev_out):
+                    h_.copy_(d_, non_blocking=True)
+            for d_, h_ in zip(dev_in, host_in):
+                d_.copy_(h_, non_blocking=True)
+            stream.wait_stream(side)
+
+        copies_only()
+        barrier()
+        out["ms_per_step_copies_only"] = allmax(timed(copies_only, max(3, steps // 2), stream))
+        barrier()
 
         def step_serial():
             for d_, h_ in zip(dev_in, host_in):

@@ -84,7 +84,9 @@ cudaError_t launch_kmean(const KMeanParams& p, cudaStream_t stream) {
 }
 
 // ------------------------------------------------------------------------------------------------ quantiser
-template <int D>
+// kMean / kStale: the K tensor alone subtracts a mean and the dO tensor of the stale mode alone reads O; compiled out
+// elsewhere, the kernel needs fewer registers and more of its small CTAs fit an SM (more loads in flight).
+template <int D, bool kMean, bool kStale>
 __global__ void __launch_bounds__(128) quant_kernel(const QuantParams p) {
   constexpr int kTpr = D / 16;           // threads per token row (16 elements each)
   constexpr int kRpp = 128 / kTpr;       // rows per pass
@@ -96,17 +98,14 @@ __global__ void __launch_bounds__(128) quant_kernel(const QuantParams p) {
   const int c16 = tid % kTpr, r0 = tid / kTpr;
   const __nv_bfloat16* xb = p.x + b * p.sb + h * p.sh + static_cast<int64_t>(blk) * 32 * p.sn + c16 * 16;
 
-  float mean[16];
-  if (p.mean != nullptr) {
+  float mean[kMean ? 16 : 1];
+  if (kMean) {
     const float4* mp = reinterpret_cast<const float4*>(p.mean + static_cast<size_t>(bh) * D + c16 * 16);
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const float4 v = __ldg(mp + i);
       mean[4 * i] = v.x; mean[4 * i + 1] = v.y; mean[4 * i + 2] = v.z; mean[4 * i + 3] = v.w;
     }
-  } else {
-#pragma unroll
-    for (int i = 0; i < 16; ++i) mean[i] = 0.f;
   }
 
   float y[kPass][16];
@@ -118,7 +117,7 @@ __global__ void __launch_bounds__(128) quant_kernel(const QuantParams p) {
     const uint4 v0 = __ldg(src), v1 = __ldg(src + 1);
     bf16x8_to_float(v0, &y[ps][0]);
     bf16x8_to_float(v1, &y[ps][8]);
-    if (p.o != nullptr) {
+    if (kStale) {
       // stale delta = sum_d dO * O on the raw bf16 values (delta_matching/reference.py:500-501)
       const __nv_bfloat16* ob = p.o + b * p.o_sb + h * p.o_sh + (static_cast<int64_t>(blk) * 32 + r) * p.o_sn + c16 * 16;
       const uint4 o0 = __ldg(reinterpret_cast<const uint4*>(ob)), o1 = __ldg(reinterpret_cast<const uint4*>(ob) + 1);
@@ -132,9 +131,10 @@ __global__ void __launch_bounds__(128) quant_kernel(const QuantParams p) {
       for (int off = kTpr / 2; off > 0; off >>= 1) d += __shfl_xor_sync(0xffffffffu, d, off);
       if (c16 == 0) p.delta[static_cast<size_t>(bh) * p.N + blk * 32 + r] = d;
     }
+    // (x - 0) * prescale and x * prescale are the same fp32 value, so leaving the subtraction out changes no bit
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
-      y[ps][i] = (y[ps][i] - mean[i]) * p.prescale;
+      y[ps][i] = kMean ? (y[ps][i] - mean[i]) * p.prescale : y[ps][i] * p.prescale;
       amax = fmaxf(amax, fabsf(y[ps][i]));
     }
   }
@@ -162,8 +162,16 @@ __global__ void __launch_bounds__(128) quant_kernel(const QuantParams p) {
 
 cudaError_t launch_quant(const QuantParams& p, cudaStream_t stream) {
   dim3 grid(p.N / 32, p.B * p.H);
-  if (p.D == 128) quant_kernel<128><<<grid, 128, 0, stream>>>(p);
-  else quant_kernel<256><<<grid, 128, 0, stream>>>(p);
+  const bool mean = p.mean != nullptr, stale = p.o != nullptr;
+  if (p.D == 128) {
+    if (stale) quant_kernel<128, false, true><<<grid, 128, 0, stream>>>(p);
+    else if (mean) quant_kernel<128, true, false><<<grid, 128, 0, stream>>>(p);
+    else quant_kernel<128, false, false><<<grid, 128, 0, stream>>>(p);
+  } else {
+    if (stale) quant_kernel<256, false, true><<<grid, 128, 0, stream>>>(p);
+    else if (mean) quant_kernel<256, true, false><<<grid, 128, 0, stream>>>(p);
+    else quant_kernel<256, false, false><<<grid, 128, 0, stream>>>(p);
+  }
   count_launch();
   return cudaGetLastError();
 }
