@@ -4,9 +4,11 @@
 //   kernel 1 (dK/dV, key-stationary): CTA = (128-key tile, kv head, batch); loops over the query heads of the GQA group
 //     and their 128-query tiles: S^T = K8 Q8^T, dP^T = V8 dO8^T (kind::f8f6f4), P^T codes and dS^T codes written to TMEM,
 //     dV += P^T dO and dK += dS^T Q as block-scaled chains (kind::mxf8f6f4).  The group is reduced in TMEM, dK / dV are
-//     rounded to bf16 once per KV head.
-//   kernel 2 (dQ, query-stationary): CTA = (128-query tile, query head, batch); loops over key tiles: S, dP recomputed,
-//     dS codes staged in shared memory, dQ += dS K block-scaled; dQ * softmax_scale rounded to bf16 once.
+//     rounded to bf16 once per KV head.  With a workspace it also leaves the dS^T code tiles there for the streaming dQ
+//     kernel (dm_bwd_p2.cu).  Head_dim 256 runs it as two launches, one per accumulator.
+//   kernel 2 (dQ, query-stationary, the form without a workspace): CTA = (128-query tile, query head, batch); loops over
+//     key tiles: S, dP recomputed, dS codes staged in shared memory, dQ += dS K block-scaled; dQ * softmax_scale rounded
+//     to bf16 once.
 //
 // Numerics (delta_matching/reference.py:476-518 with preset "sm100-mx", :612-613; kernel-side rules
 // delta_matching/sm100/dm_bwd_sm100.py:5413-5433, 6175-6224 and attention_math_sm100.py:26-45):
@@ -41,330 +43,25 @@ __device__ __forceinline__ void store_bf16_chunk(const uint32_t (&r)[32], float 
   for (int e = 0; e < 4; ++e) d4[e] = make_uint4(w[4 * e], w[4 * e + 1], w[4 * e + 2], w[4 * e + 3]);
 }
 
-// ================================================================================================ dK / dV
-template <int D, bool DV, bool DK>
-struct KvCfg {
-  static constexpr int kSub = D / 128;
-  static constexpr int kTileBytes = 128 * D;
-  static constexpr int kStages = 2;
-  static constexpr int kTmemCols = 512;
-  static constexpr int kColS = 0;            // S^T fp32; P^T codes reuse columns 0-31
-  static constexpr int kColSfaV = 32;        // 4 columns: SFA word of the dV chain (written after S^T is consumed)
-  static constexpr int kColOne = 36;         // 4 columns of 0x7F7F7F7F: scale 1.0 for the B operand
-  static constexpr int kColDp = 128;         // dP^T fp32; dS^T codes reuse columns 128-159
-  static constexpr int kColSfaK = 160;       // 4 columns: SFA word of the dK chain
-  static constexpr int kColDv = 256;                         // D columns when DV
-  static constexpr int kColDk = DV ? 256 + D : 256;          // D columns when DK
-  static_assert(kColDk + (DK ? D : 0) <= 512, "TMEM budget");
-  static constexpr int kSmemK = 0;
-  static constexpr int kSmemV = kTileBytes;
-  static constexpr int kSmemQ = 2 * kTileBytes;                      // [kStages]
-  static constexpr int kSmemDo = kSmemQ + kStages * kTileBytes;      // [kStages]
-  static constexpr int kSmemVec = kSmemDo + kStages * kTileBytes;    // 2 x (l2[128], delta[128]) floats
-  static constexpr int kSmemWs = kSmemVec + 2 * 2 * 128 * 4;         // dS^T codes of the iteration for the workspace (DK)
-  static constexpr int kSmemBar = kSmemWs + (DK ? 16384 : 0);
-  static constexpr int kSmemBytes = kSmemBar + 256 + 1024;
-  static_assert(kSmemBytes <= 232448, "shared memory budget");
-};
-
-template <int D, bool DV, bool DK>
-__global__ void __launch_bounds__(192, 1)
-bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
-                const __grid_constant__ CUtensorMap tm_ds, const BwdParams p) {
-  using C = KvCfg<D, DV, DK>;
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* sK = smem + C::kSmemK;
-  uint8_t* sV = smem + C::kSmemV;
-  uint8_t* sQ = smem + C::kSmemQ;
-  uint8_t* sDo = smem + C::kSmemDo;
-  float* sVec = reinterpret_cast<float*>(smem + C::kSmemVec);
-  uint8_t* sWs = smem + C::kSmemWs;
-  // the DK launch of the two-pass backward also leaves the dS^T codes in the workspace (pass 2 computes dQ from them)
-  const bool ws = DK && p.ds_codes != nullptr;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kSmemBar);
-  uint64_t* bar_kv = bars + 0;
-  uint64_t* bar_s = bars + 1;       // S^T, dP^T ready
-  uint64_t* bar_p = bars + 2;       // codes and scale words written (128 arrivals)
-  uint64_t* bar_done = bars + 3;    // dV / dK chains of the iteration done
-  uint64_t* full = bars + 4;        // [kStages]
-  uint64_t* empty = bars + 6;       // [kStages]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 11);
-
-  const int tid = threadIdx.x, warp = tid >> 5;
-  const int n_t = p.N / 128;
-  const int kt = blockIdx.x;                          // causal: tile 0 has the most query tiles and starts first
-  const int bhk = blockIdx.y;
-  const int b = bhk / p.Hk, hk = bhk % p.Hk;
-  const int rep = p.H / p.Hk;
-  const int qt0 = p.causal ? kt : 0;
-  const int n_qi = n_t - qt0;
-  const int n_it = rep * n_qi;                        // iteration = (query head of the group, query tile)
-
-  if (tid == 0) {
-    mbar_init(bar_kv, 1);
-    mbar_init(bar_s, 1);
-    mbar_init(bar_p, 128);
-    mbar_init(bar_done, 1);
-    for (int s = 0; s < C::kStages; ++s) {
-      mbar_init(full + s, 1);
-      mbar_init(empty + s, 1);
-    }
-    *abort_flag = 0;
-    mbar_fence_init();
-  }
-  if (warp == 5) {
-    tmem_alloc(tmem_slot, C::kTmemCols);
-    tmem_relinquish();
-    tc_fence_before();
-  }
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem = *tmem_slot;
-
-  if (warp == 4) {
-    // ------------------------------------------------------------------------------------------ TMA producer
-    if (elect_one()) {
-      tma_prefetch_desc(&tm_q);
-      tma_prefetch_desc(&tm_k);
-      tma_prefetch_desc(&tm_v);
-      tma_prefetch_desc(&tm_do);
-      mbar_expect_tx(bar_kv, 2 * C::kTileBytes);
-      for (int s = 0; s < C::kSub; ++s) {
-        tma_load_2d(sK + s * 16384, &tm_k, bar_kv, s * 128, bhk * p.N + kt * 128);
-        tma_load_2d(sV + s * 16384, &tm_v, bar_kv, s * 128, bhk * p.N + kt * 128);
-      }
-      for (int it = 0; it < n_it; ++it) {
-        const int st = it % C::kStages;
-        if (it >= C::kStages) {
-          if (!wait_or_abort(empty + st, ((it / C::kStages) - 1) & 1, abort_flag)) {
-            raise_abort(abort_flag, p.status, kStatusTimeoutProducer);
-            break;
-          }
-        }
-        const int h = hk * rep + it / n_qi;
-        const int row = (b * p.H + h) * p.N + (qt0 + it % n_qi) * 128;
-        mbar_expect_tx(full + st, 2 * C::kTileBytes);
-        for (int s = 0; s < C::kSub; ++s) {
-          tma_load_2d(sQ + st * C::kTileBytes + s * 16384, &tm_q, full + st, s * 128, row);
-          tma_load_2d(sDo + st * C::kTileBytes + s * 16384, &tm_do, full + st, s * 128, row);
-        }
-      }
-    }
-  } else if (warp == 5) {
-    // ------------------------------------------------------------------------------------------ MMA issuer
-    if (elect_one()) {
-      constexpr uint32_t kIdesc = idesc_f8(128, 128, false, false);
-      const uint32_t k_lo = desc_lo(smem_u32(sK)), v_lo = desc_lo(smem_u32(sV));
-      const uint32_t q_lo0 = desc_lo(smem_u32(sQ)), do_lo0 = desc_lo(smem_u32(sDo));
-      bool ok = wait_or_abort(bar_kv, 0, abort_flag);
-      for (int it = 0; ok && it < n_it; ++it) {
-        const int st = it % C::kStages;
-        if (!(ok = wait_or_abort(full + st, (it / C::kStages) & 1, abort_flag))) break;
-        // the previous chains still read the code and scale columns that the next S^T / dP^T overwrite
-        if (it > 0 && !(ok = wait_or_abort(bar_done, (it - 1) & 1, abort_flag))) break;
-        tc_fence_after();
-        const uint32_t q_lo = q_lo0 + st * (C::kTileBytes >> 4), do_lo = do_lo0 + st * (C::kTileBytes >> 4);
-#pragma unroll
-        for (int ks = 0; ks < D / 32; ++ks) {
-          const uint32_t off = (ks / 4) * 1024 + (ks % 4) * 2;      // descriptor units of 16 bytes
-          mma_f8_ss(tmem + C::kColS, k_lo + off, q_lo + off, kIdesc, ks > 0);
-        }
-        if (DK) {
-#pragma unroll
-          for (int ks = 0; ks < D / 32; ++ks) {
-            const uint32_t off = (ks / 4) * 1024 + (ks % 4) * 2;
-            mma_f8_ss(tmem + C::kColDp, v_lo + off, do_lo + off, kIdesc, ks > 0);
-          }
-        }
-        tc_commit(bar_s);
-        if (!(ok = wait_or_abort(bar_p, it & 1, abort_flag))) break;
-        tc_fence_after();
-#pragma unroll
-        for (int ks = 0; ks < 4; ++ks) {
-#pragma unroll
-          for (int s = 0; s < C::kSub; ++s) {
-            // contraction over the 128 queries of the tile: B = dO / Q tile read MN-major, 32 query rows per step
-            if (DV)
-              mma_mxf8_ts(tmem + C::kColDv + s * 128, tmem + C::kColS + ks * 8, do_lo + s * 1024 + ks * 256,
-                          idesc_mxf8(128, 128, false, true, ks, ks), tmem + C::kColSfaV, tmem + C::kColOne,
-                          (it > 0) || (ks > 0));
-            if (DK)
-              mma_mxf8_ts(tmem + C::kColDk + s * 128, tmem + C::kColDp + ks * 8, q_lo + s * 1024 + ks * 256,
-                          idesc_mxf8(128, 128, false, true, ks, ks), tmem + C::kColSfaK, tmem + C::kColOne,
-                          (it > 0) || (ks > 0));
-          }
-        }
-        if (ws) {
-          // the compute warps left the dS^T codes of this iteration in the staging tile: send it to the workspace.  The
-          // store has read the tile before bar_done is committed, which is what the warps wait for before the next
-          // iteration's codes.
-          const int hq_it = hk * rep + it / n_qi, qt_it = qt0 + it % n_qi;
-          const int ws_tile = ((b * p.H + hq_it) * n_t + qt_it) * n_t + kt;
-          tma_store_2d(&tm_ds, sWs, 0, ws_tile * 128);
-          bulk_commit_group();
-          bulk_wait_group_read<0>();
-        }
-        tc_commit(empty + st);
-        tc_commit(bar_done);
-      }
-      if (ws) bulk_wait_group<0>();
-      if (!ok) raise_abort(abort_flag, p.status, kStatusTimeoutMma);
-    }
-  } else {
-    // ------------------------------------------------------------------------------------------ compute warps
-    const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
-    const int key = kt * 128 + tid;
-    const int nblk = p.N / 32;
-    const float ks_row = p.ks[static_cast<size_t>(bhk) * nblk + key / 32];
-    const float vs_row = p.vs[static_cast<size_t>(bhk) * nblk + key / 32];
-    bool ok = true;
-    for (int it = 0; it < n_it; ++it) {
-      const int h = hk * rep + it / n_qi;
-      const int qt = qt0 + it % n_qi;
-      const int bh = b * p.H + h;
-      float* l2 = sVec + (it & 1) * 256;
-      float* dl = l2 + 128;
-      l2[tid] = p.lse[static_cast<size_t>(bh) * p.N + qt * 128 + tid] * kLog2e;
-      dl[tid] = p.delta[static_cast<size_t>(bh) * p.N + qt * 128 + tid];
-      const float4 qs4 = *reinterpret_cast<const float4*>(p.qs + static_cast<size_t>(bh) * nblk + qt * 4);
-      const float4 dos4 = *reinterpret_cast<const float4*>(p.dos + static_cast<size_t>(bh) * nblk + qt * 4);
-      const float qsv[4] = {qs4.x, qs4.y, qs4.z, qs4.w};
-      const float dosv[4] = {dos4.x, dos4.y, dos4.z, dos4.w};
-      const bool diag = p.causal && (qt == kt);
-      bar_sync(1, 128);
-      // after a failed wait the warp keeps meeting the others at the named barrier (it only skips the work)
-      if (ok) ok = wait_warp(bar_s, it & 1, abort_flag);
-      if (!ok) continue;
-      tc_fence_after();
-      float ds[DK ? 128 : 1];
-      float ds_amax = 0.f;
-      uint32_t sfa_v[4];
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        const float cc = (ks_row * qsv[c]) * kLog2e;
-        const float aa = vs_row * dosv[c];
-        uint32_t rs[32];
-        tmem_ld32(tmem + lane_base + C::kColS + 32 * c, rs);
-        tmem_wait_ld();
-        float pr[32];
-        float pmax = 0.f;
-#pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          float s = __uint_as_float(rs[e]);
-          if (diag && (tid > 32 * c + e)) s = -INFINITY;          // key index above the query index
-          pr[e] = ex2_approx(fmaf(s, cc, -l2[32 * c + e]));
-          pmax = fmaxf(pmax, pr[e]);
-        }
-        if (DV) {
-          const uint32_t psb = pow2_sb(pmax, 0u);
-          const float inv = sb_to_inv(psb);
-          uint32_t codes[8];
-#pragma unroll
-          for (int e = 0; e < 32; e += 4)
-            codes[e / 4] = cvt_e4m3x4(pr[e] * inv, pr[e + 1] * inv, pr[e + 2] * inv, pr[e + 3] * inv);
-          tmem_st8(tmem + lane_base + C::kColS + 8 * c, codes);
-          sfa_v[c] = sb_mul(psb, scale_to_sb(dosv[c]));
-        }
-        if (DK) {
-          uint32_t rd[32];
-          tmem_ld32(tmem + lane_base + C::kColDp + 32 * c, rd);
-          tmem_wait_ld();
-#pragma unroll
-          for (int e = 0; e < 32; ++e) {
-            const float v = pr[e] * (__uint_as_float(rd[e]) * aa - dl[32 * c + e]);
-            ds[32 * c + e] = v;
-            ds_amax = fmaxf(ds_amax, fabsf(v));
-          }
-        }
-      }
-      if (DV) {
-        const uint32_t w = pack4(sfa_v[0], sfa_v[1], sfa_v[2], sfa_v[3]);
-        tmem_st4(tmem + lane_base + C::kColSfaV, w, w, w, w);
-      }
-      tmem_st4(tmem + lane_base + C::kColOne, 0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu);
-      if (DK) {
-        // one scale for the (128 queries x this warp's 32 keys) block
-        const uint32_t dsb = pow2_sb(warp_max(ds_amax), 127u);
-        const float inv = sb_to_inv(dsb);
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t codes[8];
-#pragma unroll
-          for (int e = 0; e < 32; e += 4)
-            codes[e / 4] = cvt_e4m3x4(ds[32 * c + e] * inv, ds[32 * c + e + 1] * inv, ds[32 * c + e + 2] * inv,
-                                      ds[32 * c + e + 3] * inv);
-          tmem_st8(tmem + lane_base + C::kColDp + 8 * c, codes);
-          if (ws) {
-            // the same codes as row `tid` of a [key][query] tile in 128-byte-swizzled shared memory (16-byte chunk j at
-            // chunk j ^ (tid % 8)): the layout pass 2 reads as an MN-major A operand
-            sts_u4(sWs + tid * 128 + (((2 * c) ^ (tid & 7)) << 4), codes[0], codes[1], codes[2], codes[3]);
-            sts_u4(sWs + tid * 128 + (((2 * c + 1) ^ (tid & 7)) << 4), codes[4], codes[5], codes[6], codes[7]);
-          }
-        }
-        const uint32_t w = pack4(sb_mul(dsb, scale_to_sb(qsv[0])), sb_mul(dsb, scale_to_sb(qsv[1])),
-                                 sb_mul(dsb, scale_to_sb(qsv[2])), sb_mul(dsb, scale_to_sb(qsv[3])));
-        tmem_st4(tmem + lane_base + C::kColSfaK, w, w, w, w);
-        if (ws) {
-          fence_async_smem();
-          if ((tid & 31) == 0) {
-            const size_t ws_tile = (static_cast<size_t>(bh) * n_t + qt) * n_t + kt;
-            p.ds_words[ws_tile * 4 + warp] = static_cast<uint8_t>(dsb);
-          }
-        }
-      }
-      tmem_wait_st();
-      tc_fence_before();
-      mbar_arrive(bar_p);
-    }
-    if (ok) ok = wait_warp(bar_done, (n_it - 1) & 1, abort_flag);
-    if (!ok) {
-      raise_abort(abort_flag, p.status, kStatusTimeoutCompute);
-    } else {
-      tc_fence_after();
-      if (DV) {
-        __nv_bfloat16* dst = p.dv + static_cast<int64_t>(b) * p.dv_sb + static_cast<int64_t>(key) * p.dv_sn +
-                             static_cast<int64_t>(hk) * p.dv_sh;
-#pragma unroll 1
-        for (int c = 0; c < D / 32; ++c) {
-          uint32_t r[32];
-          tmem_ld32(tmem + lane_base + C::kColDv + 32 * c, r);
-          tmem_wait_ld();
-          store_bf16_chunk(r, 1.0f, dst + 32 * c);
-        }
-      }
-      if (DK) {
-        __nv_bfloat16* dst = p.dk + static_cast<int64_t>(b) * p.dk_sb + static_cast<int64_t>(key) * p.dk_sn +
-                             static_cast<int64_t>(hk) * p.dk_sh;
-#pragma unroll 1
-        for (int c = 0; c < D / 32; ++c) {
-          uint32_t r[32];
-          tmem_ld32(tmem + lane_base + C::kColDk + 32 * c, r);
-          tmem_wait_ld();
-          store_bf16_chunk(r, 1.0f, dst + 32 * c);
-        }
-      }
-    }
-  }
-  tc_fence_before();
-  __syncthreads();
-  if (warp == 5) tmem_dealloc(tmem, C::kTmemCols);
-}
-
-
-// ================================================================================================ dK / dV, pipelined (D = 128)
+// ================================================================================================ dK / dV, pipelined
 // One CTA per SM: G compute groups of four warps (G = 2 or 4; group g owns the query blocks [g * 4/G, (g+1) * 4/G) of
 // every tile, 32 query columns per block; thread t % 128 = key row = TMEM lane), then one TMA warp and one MMA warp.
 // TMEM: one 128-column region is time-shared by S^T and dP^T (each is pulled into registers as soon as it lands, which
 // frees the region for the other), P^T codes, dS^T codes and the scale words have columns of their own, dV and dK
 // accumulate over all (query head of the group, query tile) iterations.  The tensor pipe therefore runs dP^T(i),
 // dV(i), S^T(i+1), dK(i) behind the exponentials of tile i.
-template <int G>
+//
+// Head_dim 128 runs the kernel with both accumulators (DV and DK).  At head_dim 256 one accumulator fills 256 columns,
+// so the same kernel runs twice: a DV launch (S^T, P^T codes, dV: no dP^T, no dS) and a DK launch (S^T, dP^T, dS codes,
+// dK, and the dS tiles for the workspace), each with the other half of the work compiled out.
+template <int G, int D = 128, bool DV = true, bool DK = true>
 struct KvPipeCfg {
-  static constexpr int kTileBytes = 128 * 128;
-  static constexpr int kStages = 4;
+  static_assert(D == 128 ? (DV && DK) : (D == 256 && DV != DK), "128: both accumulators; 256: one per launch");
+  static constexpr int kSub = D / 128;                 // 128-byte-wide sub-tiles of an operand row
+  static constexpr int kTileBytes = 128 * D;           // K, V, Q, dO tile
+  static constexpr int kCodeBytes = 128 * 128;         // dS^T code tile (does not depend on head_dim)
+  static constexpr int kStages = (D == 128) ? 4 : 2;
+  static constexpr int kWsBufs = (D == 128) ? 2 : 1;
   static constexpr int kGroups = G;
   static constexpr int kChunks = 4 / G;      // 32-column query blocks per thread and tile
   static constexpr int kThreads = kGroups * 128 + 64;
@@ -375,24 +72,25 @@ struct KvPipeCfg {
   static constexpr int kColXv = 192;         // 4 x 4 columns: dV scale word of query block b (byte 0)
   static constexpr int kColXk = 208;         // 4 x 4 columns: dK scale word of query block b
   static constexpr int kColOne = 224;        // 4 columns of 0x7F7F7F7F
-  static constexpr int kColDv = 256, kColDk = 384;
+  static constexpr int kColDv = 256, kColDk = (D == 128) ? 384 : 256;
   static constexpr int kSmemK = 0;
   static constexpr int kSmemV = kTileBytes;
   static constexpr int kSmemQ = 2 * kTileBytes;                      // [kStages]
   static constexpr int kSmemDo = kSmemQ + kStages * kTileBytes;      // [kStages]
   static constexpr int kSmemVec = kSmemDo + kStages * kTileBytes;    // [kStages] x (lse[128], delta[128]) floats
   static constexpr int kSmemWs = kSmemVec + kStages * 1024;          // 2 staging tiles of dS^T codes for the workspace
-  static constexpr int kSmemXch = kSmemWs + 2 * kTileBytes;          // 2 x [16 warps] floats
+  static constexpr int kSmemXch = kSmemWs + kWsBufs * kCodeBytes;    // 2 x [16 warps] floats
   static constexpr int kSmemBar = kSmemXch + 2 * 16 * 4;
   static constexpr int kSmemBytes = kSmemBar + 256 + 1024;
+  static_assert(kSmemBytes <= 232448, "shared memory budget");
 };
 
-template <int G>
-__global__ void __launch_bounds__(KvPipeCfg<G>::kThreads, 1)
+template <int G, int D, bool DV, bool DK>
+__global__ void __launch_bounds__(KvPipeCfg<G, D, DV, DK>::kThreads, 1)
 bwd_dkdv_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                      const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
                      const __grid_constant__ CUtensorMap tm_ds, const BwdParams p) {
-  using C = KvPipeCfg<G>;
+  using C = KvPipeCfg<G, D, DV, DK>;
   constexpr int kW = C::kGroups * 4;                 // compute warps; warp kW = TMA, kW + 1 = MMA
   constexpr int CH = C::kChunks;
   extern __shared__ uint8_t smem_raw[];
@@ -461,8 +159,10 @@ bwd_dkdv_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       tma_prefetch_desc(&tm_v);
       tma_prefetch_desc(&tm_do);
       mbar_expect_tx(bar_kv, 2 * C::kTileBytes);
-      tma_load_2d(sK, &tm_k, bar_kv, 0, bhk * p.N + kt * 128);
-      tma_load_2d(sV, &tm_v, bar_kv, 0, bhk * p.N + kt * 128);
+      for (int s = 0; s < C::kSub; ++s) {
+        tma_load_2d(sK + s * 16384, &tm_k, bar_kv, s * 128, bhk * p.N + kt * 128);
+        tma_load_2d(sV + s * 16384, &tm_v, bar_kv, s * 128, bhk * p.N + kt * 128);
+      }
       int h = hk * rep, qi = 0;
       for (int it = 0; it < n_it; ++it) {
         const int st = it % C::kStages;
@@ -474,8 +174,10 @@ bwd_dkdv_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         }
         const size_t row = static_cast<size_t>(b * p.H + h) * p.N + (qt0 + qi) * 128;
         mbar_expect_tx(full + st, 2 * C::kTileBytes + 1024);
-        tma_load_2d(sQ + st * C::kTileBytes, &tm_q, full + st, 0, static_cast<int>(row));
-        tma_load_2d(sDo + st * C::kTileBytes, &tm_do, full + st, 0, static_cast<int>(row));
+        for (int s = 0; s < C::kSub; ++s) {
+          tma_load_2d(sQ + st * C::kTileBytes + s * 16384, &tm_q, full + st, s * 128, static_cast<int>(row));
+          tma_load_2d(sDo + st * C::kTileBytes + s * 16384, &tm_do, full + st, s * 128, static_cast<int>(row));
+        }
         bulk_load_1d(sVec + st * 256, p.lse + row, 512, full + st);
         bulk_load_1d(sVec + st * 256 + 128, p.delta + row, 512, full + st);
         if (++qi == n_qi) {
@@ -491,55 +193,74 @@ bwd_dkdv_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       constexpr uint32_t kIdescBs = idesc_mxf8(128, 128, false, true, 0, 0);
       const uint32_t k_lo = desc_lo(smem_u32(sK)), v_lo = desc_lo(smem_u32(sV));
       const uint32_t q_lo0 = desc_lo(smem_u32(sQ)), do_lo0 = desc_lo(smem_u32(sDo));
+      // a first matmul of the tile: both operands K-major, D / 32 steps of 32 bytes inside the 128-byte swizzle rows
+      auto chain_kmajor = [&](uint32_t a_lo, uint32_t b_lo) {
+#pragma unroll
+        for (int ks = 0; ks < D / 32; ++ks) {
+          const uint32_t off = (ks / 4) * 1024 + (ks % 4) * 2;        // descriptor units of 16 bytes
+          mma_f8_ss(tmem + C::kColSd, a_lo + off, b_lo + off, kIdesc, ks > 0);
+        }
+      };
+      // a second matmul: A = codes in TMEM (8 columns per 32-query step), B = dO / Q tile MN-major (32 query rows per
+      // step), one 128-column accumulator slice per sub-tile of head_dim
+      auto chain_acc = [&](uint32_t d_col, uint32_t a_col, uint32_t b_lo, uint32_t x_col, bool first) {
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) {
+#pragma unroll
+          for (int s = 0; s < C::kSub; ++s)
+            mma_mxf8_ts(tmem + d_col + s * 128, tmem + a_col + ks * 8, b_lo + s * 1024 + ks * 256, kIdescBs,
+                        tmem + x_col + 4 * ks, tmem + C::kColOne, !first || (ks > 0));
+        }
+      };
       bool ok = wait_or_abort(bar_kv, 0, abort_flag);
       if (ok) ok = wait_or_abort(full + 0, 0, abort_flag);
       if (ok) {
         tc_fence_after();
-#pragma unroll
-        for (int ks = 0; ks < 4; ++ks) mma_f8_ss(tmem + C::kColSd, k_lo + ks * 2, q_lo0 + ks * 2, kIdesc, ks > 0);
+        chain_kmajor(k_lo, q_lo0);
         tc_commit(bar_s);
       }
       for (int it = 0; ok && it < n_it; ++it) {
         const int st = it % C::kStages;
         const uint32_t q_lo = q_lo0 + st * (C::kTileBytes >> 4), do_lo = do_lo0 + st * (C::kTileBytes >> 4);
         const uint32_t ph = it & 1;
+        auto next_st = [&]() -> bool {                         // S^T of the next iteration into the shared region
+          if (it + 1 >= n_it) return true;
+          const int sn = (it + 1) % C::kStages;
+          if (!wait_or_abort(full + sn, ((it + 1) / C::kStages) & 1, abort_flag)) return false;
+          tc_fence_after();
+          chain_kmajor(k_lo, q_lo0 + sn * (C::kTileBytes >> 4));
+          tc_commit(bar_s);
+          return true;
+        };
         if (!(ok = wait_or_abort(bar_sfree, ph, abort_flag))) break;
         tc_fence_after();
-#pragma unroll
-        for (int ks = 0; ks < 4; ++ks) mma_f8_ss(tmem + C::kColSd, v_lo + ks * 2, do_lo + ks * 2, kIdesc, ks > 0);
-        tc_commit(bar_dp);
-        if (!(ok = wait_or_abort(bar_pv, ph, abort_flag))) break;
-        tc_fence_after();
-        // dV += P^T dO: A = P^T codes in TMEM (8 columns per 32-query step), B = dO tile MN-major (32 query rows per step)
-#pragma unroll
-        for (int ks = 0; ks < 4; ++ks)
-          mma_mxf8_ts(tmem + C::kColDv, tmem + C::kColPc + ks * 8, do_lo + ks * 256, kIdescBs, tmem + C::kColXv + 4 * ks,
-                      tmem + C::kColOne, (it > 0) || (ks > 0));
-        if (!(ok = wait_or_abort(bar_dpfree, ph, abort_flag))) break;
-        if (it + 1 < n_it) {
-          const int sn = (it + 1) % C::kStages;
-          if (!(ok = wait_or_abort(full + sn, ((it + 1) / C::kStages) & 1, abort_flag))) break;
-          tc_fence_after();
-          const uint32_t qn_lo = q_lo0 + sn * (C::kTileBytes >> 4);
-#pragma unroll
-          for (int ks = 0; ks < 4; ++ks) mma_f8_ss(tmem + C::kColSd, k_lo + ks * 2, qn_lo + ks * 2, kIdesc, ks > 0);
-          tc_commit(bar_s);
+        if (DK) {
+          chain_kmajor(v_lo, do_lo);                           // dP^T = V dO^T into the region S^T has just left
+          tc_commit(bar_dp);
+        } else {
+          if (!(ok = next_st())) break;                        // no dP^T in a DV launch: the region is free at once
         }
-        if (!(ok = wait_or_abort(bar_pk, ph, abort_flag))) break;
-        tc_fence_after();
-#pragma unroll
-        for (int ks = 0; ks < 4; ++ks)
-          mma_mxf8_ts(tmem + C::kColDk, tmem + C::kColDc + ks * 8, q_lo + ks * 256, kIdescBs, tmem + C::kColXk + 4 * ks,
-                      tmem + C::kColOne, (it > 0) || (ks > 0));
-        if (p.ds_codes != nullptr) {
-          // The compute warps also left the dS^T codes of this iteration in staging tile it & 1: send it to the
-          // workspace.  Before the commit of bar_done below, at most this store still reads shared memory, so a warp
-          // that has seen bar_done of iteration it may overwrite staging tile (it + 1) & 1.
-          const int hq_it = hk * rep + it / n_qi, qt_it = qt0 + it % n_qi;
-          const int ws_tile = ((b * p.H + hq_it) * n_t + qt_it) * n_t + kt;
-          tma_store_2d(&tm_ds, sWs + (it & 1) * C::kTileBytes, 0, ws_tile * 128);
-          bulk_commit_group();
-          bulk_wait_group_read<1>();
+        if (DV) {
+          if (!(ok = wait_or_abort(bar_pv, ph, abort_flag))) break;
+          tc_fence_after();
+          chain_acc(C::kColDv, C::kColPc, do_lo, C::kColXv, it == 0);       // dV += P^T dO
+        }
+        if (DK) {
+          if (!(ok = wait_or_abort(bar_dpfree, ph, abort_flag))) break;
+          if (!(ok = next_st())) break;
+          if (!(ok = wait_or_abort(bar_pk, ph, abort_flag))) break;
+          tc_fence_after();
+          chain_acc(C::kColDk, C::kColDc, q_lo, C::kColXk, it == 0);        // dK += dS^T Q
+          if (p.ds_codes != nullptr) {
+            // The compute warps also left the dS^T codes of this iteration in a staging tile: send it to the workspace.
+            // Before the commit of bar_done below every earlier store has read its tile (with two tiles, all but this
+            // one), and a warp waits for bar_done of iteration it before it writes the staging tile of it + 1.
+            const int hq_it = hk * rep + it / n_qi, qt_it = qt0 + it % n_qi;
+            const int ws_tile = ((b * p.H + hq_it) * n_t + qt_it) * n_t + kt;
+            tma_store_2d(&tm_ds, sWs + (it % C::kWsBufs) * C::kCodeBytes, 0, ws_tile * 128);
+            bulk_commit_group();
+            bulk_wait_group_read<C::kWsBufs - 1>();
+          }
         }
         tc_commit(empty + st);
         tc_commit(bar_done);
@@ -610,7 +331,7 @@ bwd_dkdv_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         tc_fence_before();
         __syncwarp();
         if ((tid & 31) == 0) mbar_arrive(bar_sfree);
-        uint32_t w[CH][8], xv[CH];
+        uint32_t w[DV ? CH : 1][8], xv[DV ? CH : 1];
 #pragma unroll
         for (int c = 0; c < CH; ++c) {
           if (diag) {
@@ -632,20 +353,41 @@ bwd_dkdv_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             pm0 = max3(pm0, pr[c][e].x, pr[c][e].y);
             pm1 = max3(pm1, pr[c][e + 1].x, pr[c][e + 1].y);
           }
-          // P^T codes: one power-of-two scale per (key row, 32 queries) = per thread, block and tile
-          const uint32_t psb = pow2_sb(fmaxf(pm0, pm1), 0u);
-          codes32(pr[c], sb_to_inv(psb), w[c]);
-          xv[c] = sb_mul(psb, scale_to_sb(dos_c[c]));
+          if (DV) {
+            // P^T codes: one power-of-two scale per (key row, 32 queries) = per thread, block and tile
+            const uint32_t psb = pow2_sb(fmaxf(pm0, pm1), 0u);
+            codes32(pr[c], sb_to_inv(psb), w[c]);
+            xv[c] = sb_mul(psb, scale_to_sb(dos_c[c]));
+          }
         }
         if (it > 0) ok = wait_warp(bar_done, ph ^ 1, abort_flag);   // the previous chains have read codes and words
         if (ok) {
+          if (DV) {
 #pragma unroll
-          for (int c = 0; c < CH; ++c) {
-            tmem_st8(tmem + lane_base + C::kColPc + 8 * (blk0 + c), w[c]);
-            tmem_st4(tmem + lane_base + C::kColXv + 4 * (blk0 + c), xv[c], xv[c], xv[c], xv[c]);
+            for (int c = 0; c < CH; ++c) {
+              tmem_st8(tmem + lane_base + C::kColPc + 8 * (blk0 + c), w[c]);
+              tmem_st4(tmem + lane_base + C::kColXv + 4 * (blk0 + c), xv[c], xv[c], xv[c], xv[c]);
+            }
           }
           if (wg == 0) tmem_st4(tmem + lane_base + C::kColOne, 0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu);
+          if (!DK) {                                       // a DV launch has no second half: the codes are the hand-off
+            tmem_wait_st();
+            tc_fence_before();
+            __syncwarp();
+            if ((tid & 31) == 0) mbar_arrive(bar_pv);
+          }
         }
+      }
+      if (!DK) {                                           // DV launch: on to the next tile
+        if (++st == C::kStages) {
+          st = 0;
+          st_ph ^= 1;
+        }
+        if (++qi == n_qi) {
+          qi = 0;
+          ++hq;
+        }
+        continue;
       }
       // dP^T (its chain was issued when S^T was handed back) is requested while the code stores are still in flight
       if (ok) ok = wait_warp(bar_dp, ph, abort_flag);
@@ -654,10 +396,12 @@ bwd_dkdv_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         uint32_t rd[CH][32];
 #pragma unroll
         for (int c = 0; c < CH; ++c) tmem_ld32(tmem + lane_base + C::kColSd + 32 * (blk0 + c), rd[c]);
-        tmem_wait_st();
-        tc_fence_before();
-        __syncwarp();
-        if ((tid & 31) == 0) mbar_arrive(bar_pv);
+        if (DV) {
+          tmem_wait_st();
+          tc_fence_before();
+          __syncwarp();
+          if ((tid & 31) == 0) mbar_arrive(bar_pv);
+        }
         tmem_wait_ld();
         tc_fence_before();
         __syncwarp();
@@ -711,7 +455,7 @@ bwd_dkdv_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         if (p.ds_codes != nullptr) {
           // the same codes as a [key][query] tile in 128-byte-swizzled shared memory (16-byte chunk j of row r at
           // chunk j ^ (r % 8)); the MMA warp's thread stores the tile to the workspace for pass 2
-          const uint32_t ws_row = ws_a + ph * C::kTileBytes + r * 128;
+          const uint32_t ws_row = ws_a + (it % C::kWsBufs) * C::kCodeBytes + r * 128;
           const int j = 2 * (blk0 + c);
           sts_u4(ws_row + ((j ^ (r & 7)) << 4), w[0], w[1], w[2], w[3]);
           sts_u4(ws_row + (((j + 1) ^ (r & 7)) << 4), w[4], w[5], w[6], w[7]);
@@ -729,17 +473,23 @@ bwd_dkdv_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       raise_abort(abort_flag, p.status, kStatusTimeoutCompute);
     } else {
       tc_fence_after();
+      // every group writes its 32-column blocks of each 128-column slice of the accumulators
 #pragma unroll 1
-      for (int c = 0; c < CH; ++c) {
+      for (int cc = 0; cc < C::kSub * CH; ++cc) {
+        const int col = 128 * (cc / CH) + 32 * (blk0 + cc % CH);
         uint32_t rr[32];
-        tmem_ld32(tmem + lane_base + C::kColDv + 32 * (blk0 + c), rr);
-        tmem_wait_ld();
-        store_bf16_chunk(rr, 1.0f, p.dv + static_cast<int64_t>(b) * p.dv_sb + static_cast<int64_t>(key) * p.dv_sn +
-                                       static_cast<int64_t>(hk) * p.dv_sh + 32 * (blk0 + c));
-        tmem_ld32(tmem + lane_base + C::kColDk + 32 * (blk0 + c), rr);
-        tmem_wait_ld();
-        store_bf16_chunk(rr, 1.0f, p.dk + static_cast<int64_t>(b) * p.dk_sb + static_cast<int64_t>(key) * p.dk_sn +
-                                       static_cast<int64_t>(hk) * p.dk_sh + 32 * (blk0 + c));
+        if (DV) {
+          tmem_ld32(tmem + lane_base + C::kColDv + col, rr);
+          tmem_wait_ld();
+          store_bf16_chunk(rr, 1.0f, p.dv + static_cast<int64_t>(b) * p.dv_sb + static_cast<int64_t>(key) * p.dv_sn +
+                                         static_cast<int64_t>(hk) * p.dv_sh + col);
+        }
+        if (DK) {
+          tmem_ld32(tmem + lane_base + C::kColDk + col, rr);
+          tmem_wait_ld();
+          store_bf16_chunk(rr, 1.0f, p.dk + static_cast<int64_t>(b) * p.dk_sb + static_cast<int64_t>(key) * p.dk_sn +
+                                         static_cast<int64_t>(hk) * p.dk_sh + col);
+        }
       }
     }
   }
@@ -1334,36 +1084,28 @@ static cudaError_t set_smem(K kernel, int bytes, bool* done) {
 }
 
 template <int D, bool DV, bool DK>
-static cudaError_t launch_kv_t(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
-                               const CUtensorMap& tdo, const CUtensorMap& tds, const BwdParams& p, cudaStream_t stream) {
-  using C = KvCfg<D, DV, DK>;
+static cudaError_t launch_kv_pipe_t(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
+                                    const CUtensorMap& tdo, const CUtensorMap& tds, const BwdParams& p,
+                                    cudaStream_t stream) {
+  using C = KvPipeCfg<4, D, DV, DK>;
   static bool done[64] = {};
-  cudaError_t e = set_smem(bwd_dkdv_kernel<D, DV, DK>, C::kSmemBytes, done);
+  cudaError_t e = set_smem(bwd_dkdv_pipe_kernel<4, D, DV, DK>, C::kSmemBytes, done);
   if (e != cudaSuccess) return e;
   dim3 grid(p.N / 128, p.B * p.Hk);
-  bwd_dkdv_kernel<D, DV, DK><<<grid, 192, C::kSmemBytes, stream>>>(tq, tk, tv, tdo, tds, p);
+  bwd_dkdv_pipe_kernel<4, D, DV, DK><<<grid, C::kThreads, C::kSmemBytes, stream>>>(tq, tk, tv, tdo, tds, p);
   count_launch();
   return cudaGetLastError();
 }
-
 
 cudaError_t launch_bwd_dkdv(int D, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                             const CUtensorMap& tdo, const CUtensorMap* tds_or_null, const BwdParams& p,
                             cudaStream_t stream) {
   const CUtensorMap* tds = (tds_or_null != nullptr) ? tds_or_null : &tq;     // unused by the kernel without a workspace
-  if (D == 128) {
-    dim3 grid(p.N / 128, p.B * p.Hk);
-    static bool done[64] = {};
-    cudaError_t e = set_smem(bwd_dkdv_pipe_kernel<4>, KvPipeCfg<4>::kSmemBytes, done);
-    if (e != cudaSuccess) return e;
-    bwd_dkdv_pipe_kernel<4><<<grid, KvPipeCfg<4>::kThreads, KvPipeCfg<4>::kSmemBytes, stream>>>(tq, tk, tv, tdo, *tds, p);
-    count_launch();
-    return cudaGetLastError();
-  }
-  // head_dim 256: S^T + dP^T + dK + dV exceed the 512 TMEM columns, so dV and dK run as two launches
-  cudaError_t e = launch_kv_t<256, true, false>(tq, tk, tv, tdo, *tds, p, stream);
+  if (D == 128) return launch_kv_pipe_t<128, true, true>(tq, tk, tv, tdo, *tds, p, stream);
+  // head_dim 256: one accumulator fills 256 of the 512 TMEM columns, so dV and dK run as two launches of the same kernel
+  cudaError_t e = launch_kv_pipe_t<256, true, false>(tq, tk, tv, tdo, *tds, p, stream);
   if (e != cudaSuccess) return e;
-  return launch_kv_t<256, false, true>(tq, tk, tv, tdo, *tds, p, stream);
+  return launch_kv_pipe_t<256, false, true>(tq, tk, tv, tdo, *tds, p, stream);
 }
 
 template <int D>
