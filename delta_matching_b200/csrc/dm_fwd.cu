@@ -25,10 +25,14 @@ struct FwdCfg {
   static constexpr int kTileBytes = 128 * D;           // one 128-row operand tile
   static constexpr int kStages = 2;
   static constexpr int kTmemCols = (D == 128) ? 256 : 512;
+  // At head_dim 256 one CTA owns the SM's 512 columns, and S is double-buffered (S0 0-127, S1 128-255, O 256-511): the
+  // S chain of key tile i + 1 runs while the softmax warps work on tile i.  At head_dim 128 two CTAs share the SM with 256
+  // columns each (S 0-127, O 128-255) and take turns instead.
+  static constexpr bool kDoubleS = (D == 256);
   static constexpr int kColS = 0;                      // S accumulator, 128 fp32 columns; P codes reuse columns 0-31
   static constexpr int kColSfa = 32;                   // 4 columns, each this row's SFA word
   static constexpr int kColSfb = 36;                   // 4 columns, each the tile's V scale word
-  static constexpr int kColO = 128;                    // O accumulator, D fp32 columns
+  static constexpr int kColO = kDoubleS ? 256 : 128;   // O accumulator, D fp32 columns
   // shared memory: Q | K stages | V stages | barriers
   static constexpr int kSmemQ = 0;
   static constexpr int kSmemK = kTileBytes;
@@ -60,12 +64,16 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
   uint8_t* sV = smem + C::kSmemV;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kSmemBar);
   uint64_t* bar_q = bars + 0;
-  uint64_t* bar_s = bars + 1;     // S accumulator ready (MMA commit)
+  uint64_t* bar_s = bars + 1;     // S accumulator ready (MMA commit); with two S buffers: buffer 0
+  uint64_t* bar_s1 = bars + 11;   // S buffer 1 ready
+  uint64_t* bar_p1 = bars + 16;   // two S buffers: P codes of buffer 1 written
+  uint64_t* bar_o1 = bars + 17;   // two S buffers: PV chain out of buffer 1 done
   uint64_t* bar_p = bars + 2;     // P codes + scale words written (one arrival per softmax warp)
   uint64_t* bar_o = bars + 3;     // PV chain done (MMA commit)
   uint64_t* full_k = bars + 4;    // [kStages]
   uint64_t* full_v = bars + 6;    // [kStages]
-  uint64_t* empty = bars + 8;     // [kStages] stage free again (MMA commit)
+  uint64_t* empty_k = bars + 8;   // [kStages] K stage free again (MMA commit behind the S chain)
+  uint64_t* empty_v = bars + 14;  // [kStages] V stage free again (MMA commit behind the PV chain)
   uint64_t* bar_qfree = bars + 10; // the item's last S chain has read Q (MMA commit)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 13);
@@ -81,13 +89,17 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
   if (tid == 0) {
     mbar_init(bar_q, 1);
     mbar_init(bar_s, 1);
+    mbar_init(bar_s1, 1);
+    mbar_init(bar_p1, 4);
+    mbar_init(bar_o1, 1);
     mbar_init(bar_p, 4);
     mbar_init(bar_o, 1);
     mbar_init(bar_qfree, 1);
     for (int s = 0; s < C::kStages; ++s) {
       mbar_init(full_k + s, 1);
       mbar_init(full_v + s, 1);
-      mbar_init(empty + s, 1);
+      mbar_init(empty_k + s, 1);
+      mbar_init(empty_v + s, 1);
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -100,6 +112,14 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
+  // Barrier and phase of running tile g.  With two S buffers the S / P / PV barriers exist once per buffer and tile g is
+  // phase g / 2 of its buffer's barrier: a waiter is then never more than one phase away from the barrier it tests (with
+  // one barrier for both buffers the softmax warps, which run a tile ahead of the PV chains, could test the phase bit of
+  // chain g while chain g - 1 was still pending, and the test would pass at once).
+  auto s_bar = [&](int g) { return (C::kDoubleS && (g & 1)) ? bar_s1 : bar_s; };
+  auto p_bar = [&](int g) { return (C::kDoubleS && (g & 1)) ? bar_p1 : bar_p; };
+  auto o_bar = [&](int g) { return (C::kDoubleS && (g & 1)) ? bar_o1 : bar_o; };
+  auto tile_ph = [&](int g) -> uint32_t { return static_cast<uint32_t>(C::kDoubleS ? (g >> 1) : g) & 1u; };
 
   if (warp == 4) {
     // ------------------------------------------------------------------------------------------ TMA producer
@@ -119,11 +139,13 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         for (int s = 0; s < C::kSub; ++s) tma_load_2d(sQ + s * 16384, &tm_q, bar_q, s * 128, bh * p.N + qt * 128);
         for (int it = 0; it < n_it; ++it, ++gt) {
           const int st = gt % C::kStages;
-          if (gt >= C::kStages && !(ok = wait_or_abort(empty + st, ((gt / C::kStages) - 1) & 1, abort_flag))) break;
+          const uint32_t eph = ((gt / C::kStages) - 1) & 1;
+          if (gt >= C::kStages && !(ok = wait_or_abort(empty_k + st, eph, abort_flag))) break;
           const int row = bhk * p.N + (kt_first - it) * 128;
           mbar_expect_tx(full_k + st, C::kTileBytes);
           for (int s = 0; s < C::kSub; ++s)
             tma_load_2d(sK + st * C::kTileBytes + s * 16384, &tm_k, full_k + st, s * 128, row);
+          if (gt >= C::kStages && !(ok = wait_or_abort(empty_v + st, eph, abort_flag))) break;
           mbar_expect_tx(full_v + st, C::kTileBytes);
           for (int s = 0; s < C::kSub; ++s)
             tma_load_2d(sV + st * C::kTileBytes + s * 16384, &tm_v, full_v + st, s * 128, row);
@@ -142,25 +164,43 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         const int qt = n_qt - 1 - item / BH;
         const int n_it = p.causal ? (qt + 1) : n_qt;
         if (!(ok = wait_or_abort(bar_q, ic & 1, abort_flag))) break;
-        for (int it = 0; it < n_it; ++it, ++gt) {
-          const int st = gt % C::kStages;
-          const uint32_t ph = (gt / C::kStages) & 1;
-          if (!(ok = wait_or_abort(full_k + st, ph, abort_flag))) break;
-          // the previous PV chain (of this item or of the one before) has read its scale words out of the S columns
-          if (kOrdered && gt > 0 && !(ok = wait_or_abort(bar_o, (gt - 1) & 1, abort_flag))) break;
+        // S = Q K^T of running tile g of the CTA into S buffer `buf`: both operands K-major, k-step of 32 bytes inside
+        // the 128-byte swizzle row
+        // `prev`: a PV chain that has to be complete first (none if negative).  With one S buffer that is the chain of tile
+        // g - 1 (see kOrdered above).  With two, the chain of tile g - 2 read its codes and scale words out of this buffer;
+        // the caller names the latest chain it has issued, which is g - 2 for a look-ahead and g - 1 for the first tile of
+        // an item, which finished behind the chain of g - 2.
+        auto issue_s = [&](int g, int buf, int prev) -> bool {
+          const int st = g % C::kStages;
+          if (!wait_or_abort(full_k + st, (g / C::kStages) & 1, abort_flag)) return false;
+          if (prev >= 0 && !wait_or_abort(o_bar(prev), tile_ph(prev), abort_flag)) return false;
           tc_fence_after();
-          // S = Q K^T: both operands K-major, k-step of 32 bytes inside the 128-byte swizzle row
-          const uint32_t k_lo = k_lo0 + st * (C::kTileBytes >> 4), v_lo = v_lo0 + st * (C::kTileBytes >> 4);
+          const uint32_t k_lo = k_lo0 + st * (C::kTileBytes >> 4);
 #pragma unroll
           for (int ks = 0; ks < D / 32; ++ks) {
             const uint32_t off = (ks / 4) * 1024 + (ks % 4) * 2;      // descriptor units of 16 bytes
-            mma_f8_ss(tmem + C::kColS, q_lo + off, k_lo + off, kIdescS, ks > 0);
+            mma_f8_ss(tmem + C::kColS + 128 * buf, q_lo + off, k_lo + off, kIdescS, ks > 0);
           }
-          tc_commit(bar_s);
-          if (it == n_it - 1) tc_commit(bar_qfree);
-          if (!(ok = wait_or_abort(bar_p, gt & 1, abort_flag))) break;
+          tc_commit(s_bar(g));
+          tc_commit(empty_k + st);                             // the K stage is free as soon as this chain has read it
+          return true;
+        };
+        for (int it = 0; it < n_it; ++it, ++gt) {
+          const int st = gt % C::kStages;
+          const uint32_t ph = (gt / C::kStages) & 1;
+          const int buf = C::kDoubleS ? (gt & 1) : 0;
+          if (!C::kDoubleS || it == 0) {
+            if (!(ok = issue_s(gt, buf, (kOrdered || C::kDoubleS) ? gt - 1 : -1))) break;
+            if (it == n_it - 1) tc_commit(bar_qfree);
+          }
+          if (C::kDoubleS && it + 1 < n_it) {                  // the next tile of the item into the other buffer, now
+            if (!(ok = issue_s(gt + 1, buf ^ 1, gt - 1))) break;
+            if (it + 1 == n_it - 1) tc_commit(bar_qfree);
+          }
+          if (!(ok = wait_or_abort(p_bar(gt), tile_ph(gt), abort_flag))) break;
           if (!(ok = wait_or_abort(full_v + st, ph, abort_flag))) break;
           tc_fence_after();
+          const uint32_t v_lo = v_lo0 + st * (C::kTileBytes >> 4);
           // O += P V: A = P codes in TMEM (8 columns per 32-key step), B = V tile MN-major (32 key rows per step).  The
           // first chain of an item overwrites O: the softmax warps signal bar_p of that tile only after they have read
           // the previous item's O.
@@ -168,14 +208,13 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
           for (int ks = 0; ks < 4; ++ks) {
 #pragma unroll
             for (int s = 0; s < C::kSub; ++s) {
-              mma_mxf8_ts(tmem + C::kColO + s * 128, tmem + C::kColS + ks * 8, v_lo + s * 1024 + ks * 256,
-                          idesc_mxf8(128, 128, false, true, ks, ks), tmem + C::kColSfa, tmem + C::kColSfb,
-                          (it > 0) || (ks > 0));
+              mma_mxf8_ts(tmem + C::kColO + s * 128, tmem + C::kColS + 128 * buf + ks * 8, v_lo + s * 1024 + ks * 256,
+                          idesc_mxf8(128, 128, false, true, ks, ks), tmem + C::kColSfa + 128 * buf,
+                          tmem + C::kColSfb + 128 * buf, (it > 0) || (ks > 0));
             }
           }
-          tc_commit(empty + st);
-          tc_commit(bar_o);
-          // The next S chain overwrites the P codes and scale words this chain reads: see kOrdered above.
+          tc_commit(empty_v + st);
+          tc_commit(o_bar(gt));
         }
       }
       if (!ok) raise_abort(abort_flag, p.status, kStatusTimeoutMma);
@@ -231,16 +270,18 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
           ks4 = *reinterpret_cast<const float4*>(item_kv(item_n, p.ks));
           vs4 = *reinterpret_cast<const float4*>(item_kv(item_n, p.vs));
         }
-        if (!wait_warp(bar_s, gt & 1, abort_flag)) return false;
+        const int sbuf = C::kDoubleS ? (gt & 1) : 0;                         // S buffer of this tile
+        const uint32_t s_col = C::kColS + 128 * sbuf;
+        if (!wait_warp(s_bar(gt), tile_ph(gt), abort_flag)) return false;
         tc_fence_after();
         float bsum[4], kb[4], bmax[4];
         uint32_t r[2][32];
-        tmem_ld32(tmem + lane_base + C::kColS, r[0]);
+        tmem_ld32(tmem + lane_base + s_col, r[0]);
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           uint32_t (&rc)[32] = r[c & 1];
           tmem_wait_ld();
-          if (c < 3) tmem_ld32(tmem + lane_base + C::kColS + 32 * (c + 1), r[(c + 1) & 1]);   // next chunk in flight
+          if (c < 3) tmem_ld32(tmem + lane_base + s_col + 32 * (c + 1), r[(c + 1) & 1]);   // next chunk in flight
           if (kDiag) {
 #pragma unroll
             for (int e = 0; e < 32; ++e)
@@ -265,7 +306,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
           }
           sum0 = add2(sum0, sum1);
           bsum[c] = sum0.x + sum0.y;
-          tmem_st8(tmem + lane_base + C::kColS + 8 * c, codes);
+          tmem_st8(tmem + lane_base + s_col + 8 * c, codes);
         }
         const float mcand = ceilf(fmaxf(fmaxf(bmax[0], bmax[1]), fmaxf(bmax[2], bmax[3])));
         float acc_scale = 1.0f;
@@ -276,7 +317,12 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
           m = mcand;
         }
         if (it > 0 && __any_sync(0xffffffffu, acc_scale != 1.0f)) {
-          // rare: the running max moved by more than 32 binades; rescale this warp's O rows in place
+          // rare: the running max moved by more than 32 binades; rescale this warp's O rows in place.  With two S
+          // buffers this tile's S was issued ahead of the previous PV chain, so that chain is waited for by name.
+          if (C::kDoubleS) {
+            if (!wait_warp(o_bar(gt - 1), tile_ph(gt - 1), abort_flag)) return false;
+            tc_fence_after();
+          }
           for (int c = 0; c < D / 32; ++c) {
             uint32_t ro[32];
             tmem_ld32(tmem + lane_base + C::kColO + 32 * c, ro);
@@ -295,18 +341,18 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
           l = fmaf(bsum[c], __uint_as_float(sb[c] << 23), l);
         }
         const uint32_t sfa = pack4(sb[0], sb[1], sb[2], sb[3]);
-        tmem_st4(tmem + lane_base + C::kColSfa, sfa, sfa, sfa, sfa);
-        tmem_st4(tmem + lane_base + C::kColSfb, sfb, sfb, sfb, sfb);
+        tmem_st4(tmem + lane_base + C::kColSfa + 128 * sbuf, sfa, sfa, sfa, sfa);
+        tmem_st4(tmem + lane_base + C::kColSfb + 128 * sbuf, sfb, sfb, sfb, sfb);
         tmem_wait_st();
         tc_fence_before();
         __syncwarp();
-        if ((tid & 31) == 0) mbar_arrive(bar_p);
+        if ((tid & 31) == 0) mbar_arrive(p_bar(gt));
         ++gt;
         return true;
       };
       ok = p.causal ? tile(0, std::true_type{}) : tile(0, std::false_type{});
       for (int it = 1; ok && it < n_it; ++it) ok = tile(it, std::false_type{});
-      if (ok) ok = wait_warp(bar_o, (gt - 1) & 1, abort_flag);
+      if (ok) ok = wait_warp(o_bar(gt - 1), tile_ph(gt - 1), abort_flag);
       if (!ok) break;
       tc_fence_after();
       const float inv_l = 1.0f / l;

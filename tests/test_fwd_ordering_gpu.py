@@ -17,7 +17,7 @@ def _codes(oracle, B, N, H, Hk, D, seed, qk_scale=1.0):
 
 
 @pytest.mark.parametrize("B,N,H,Hk,D,causal,s", [(4, 4096, 32, 8, 128, True, 1.0), (8, 2048, 16, 16, 128, False, 30.0),
-                                                 (1, 2048, 4, 4, 256, True, 1.0)])
+                                                 (1, 2048, 4, 4, 256, True, 1.0), (2, 1024, 8, 8, 256, True, 1.0)])
 def test_ordered_and_unordered_forward_agree_bitwise(B, N, H, Hk, D, causal, s, oracle):
     from delta_matching_b200 import ops
     q8, qs, k8, ks, v8, vs = _codes(oracle, B, N, H, Hk, D, seed=51, qk_scale=s)
