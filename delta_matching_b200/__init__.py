@@ -24,24 +24,29 @@ __version__ = "0.1.0"
 # the quantisation contract the kernels implement, by head dim: the reference's Blackwell presets
 # (delta_matching/reference.py:612-613, 629)
 KERNEL_NUMERICS = {"128": "sm100-mx", "256": "sm100-mx-d256"}
+# every numerics arm the kernels implement (values of dm_attn_func's `numerics`; reference.py:613-630)
+NUMERICS_ARMS = ("sm100-mx", "sm100-mx-d256", "sm100-mx-ds32", "sm100-mx-d256-ds32", "sm100-mx-nonorm")
 FA_SRC_COMMIT = "none (from-scratch sm_100a build)"
 CUTLASS_COMMIT = "none (from-scratch sm_100a build)"
 __all__ = ["dm_attn_func", "dm_attn_func_bhnd", "dm_attn_func_plain", "flash_attn_func", "blocks", "kernel_version",
-           "__version__", "KERNEL_NUMERICS"]
+           "__version__", "KERNEL_NUMERICS", "NUMERICS_ARMS"]
 
 # The reference keeps a second "plain" route as a cross-check of its Triton producers (delta_matching/core.py:178-271);
 # there is one producer implementation here, so the name is an alias.
 dm_attn_func_plain = dm_attn_func_bhnd
 
 
-def dm_attn_func(q, k, v, softmax_scale=None, causal=False, mode="matched"):
+def dm_attn_func(q, k, v, softmax_scale=None, causal=False, mode="matched", numerics="sm100-mx"):
     """Attention in the flash-attention layout: q (B, N, H, D), k / v (B, N, Hk, D) bf16 on CUDA -> o (B, N, H, D) bf16.
-    mode: "matched" (the Delta-Matching backward; needs causal=True) or "stale" (delta = rowsum(dO * O))."""
+    mode: "matched" (the Delta-Matching backward; needs causal=True) or "stale" (delta = rowsum(dO * O)).
+    numerics: "sm100-mx" (the contract; "sm100-mx-d256" names it at head_dim 256) or another arm of the reference
+    emulation's preset table that the kernels implement: "sm100-mx-ds32" / "sm100-mx-d256-ds32" (dS scaled per
+    32 x 32 block) and "sm100-mx-nonorm" (matched delta without the division by sum P); see NUMERICS_ARMS."""
     for name, t in (("q", q), ("k", k), ("v", v)):
         if not isinstance(t, torch.Tensor) or t.dim() != 4:
             raise ValueError(f"delta_matching: {name} must be a 4-D tensor (batch, seqlen, nheads, headdim)")
     return dm_attn_func_bhnd(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), causal=causal,
-                             softmax_scale=softmax_scale, delta_mode=mode)
+                             softmax_scale=softmax_scale, delta_mode=mode, numerics=numerics)
 
 
 def flash_attn_func(q, k, v, dropout_p=0.0, softmax_scale=None, causal=False, window_size=(-1, -1), softcap=0.0,
@@ -66,7 +71,7 @@ def kernel_version():
     once the library is loaded, its path (keys as delta_matching/__init__.py:80-104)."""
     from . import _lib, build
     info = {"version": __version__, "code_sha": build.code_sha(), "fa_src_commit": FA_SRC_COMMIT,
-            "numerics": dict(KERNEL_NUMERICS), "bf16_dp": False}
+            "numerics": dict(KERNEL_NUMERICS), "numerics_arms": list(NUMERICS_ARMS), "bf16_dp": False}
     if _lib.loaded_library() is not None:
         info["library"] = _lib.loaded_library()
     return info

@@ -87,13 +87,14 @@ class _DMAttn(torch.autograd.Function):
     opaque ops instead of breaking its graph here; eager calls skip the dispatcher and run the same functions directly."""
 
     @staticmethod
-    def forward(ctx, q, k, v, causal, delta_mode):
+    def forward(ctx, q, k, v, causal, delta_mode, ds32, norm):
         K = _calls()
         q8, qs, k8, ks, v8, vs, _ = K.quant_qkv(q, k, v)
         o, lse = K.fwd_fp8(q8, k8, v8, qs, ks, vs, causal)
         ctx.save_for_backward(q8, qs, k8, ks, v8, vs, o, lse)
         ctx.causal = causal
         ctx.delta_mode = delta_mode
+        ctx.ds32, ctx.norm = ds32, norm
         return o
 
     @staticmethod
@@ -106,40 +107,52 @@ class _DMAttn(torch.autograd.Function):
         do_bhnd = dO.permute(0, 2, 1, 3)                   # (B, N, H, D) -> (B, H, N, D) view, read in place
         if ctx.delta_mode == "matched":
             do8, dos, _ = K.quant_do(do_bhnd, do_bhnd, False)       # the matched mode never reads O
-            delta = K.delta_fp8(q8, k8, v8, do8, qs, ks, vs, dos, lse, ctx.causal)
+            delta = K.delta_fp8(q8, k8, v8, do8, qs, ks, vs, dos, lse, ctx.causal, ctx.norm)
         else:
             do8, dos, delta = K.quant_do(do_bhnd, o.permute(0, 2, 1, 3), True)
-        dq, dk, dv = K.bwd_fp8(q8, k8, v8, do8, qs, ks, vs, dos, lse, delta, ctx.causal)
-        return dq.permute(0, 2, 1, 3), dk.permute(0, 2, 1, 3), dv.permute(0, 2, 1, 3), None, None
+        dq, dk, dv = K.bwd_fp8(q8, k8, v8, do8, qs, ks, vs, dos, lse, delta, ctx.causal, ctx.ds32)
+        return dq.permute(0, 2, 1, 3), dk.permute(0, 2, 1, 3), dv.permute(0, 2, 1, 3), None, None, None, None
 
 
-def dm_attn_func_bhnd(q, k, v, causal=True, softmax_scale=None, delta_mode="stale"):
+def _numerics(name, D):
+    """(ds32, norm) of a numerics arm (ops.NUMERICS); the head_dim-256 names are accepted at head_dim 256 only."""
+    if name not in ops.NUMERICS:
+        raise ValueError(f"delta_matching: numerics must be one of {sorted(ops.NUMERICS)} (got {name!r})")
+    if "-d256" in name and D != 256:
+        raise ValueError(f"delta_matching: numerics {name!r} is the head_dim-256 name of its scheme (head_dim is {D})")
+    return ops.NUMERICS[name]
+
+
+def dm_attn_func_bhnd(q, k, v, causal=True, softmax_scale=None, delta_mode="stale", numerics="sm100-mx"):
     """Attention on (B, H, N, D) inputs: q (B, H, N, D), k / v (B, Hk, N, D) bf16 on CUDA (any strides; H % Hk == 0) ->
     O (B, N, H, D) bf16 contiguous.  delta_mode: "stale" (delta = rowsum(dO * O)) or "matched" (the Delta-Matching
     backward; needs causal=True).  Input errors raise ValueError / TypeError / NotImplementedError.  Works under
     torch.compile without a graph break (the kernels are registered ops with fake implementations) and under CUDA-graph
-    capture after a warm-up call."""
+    capture after a warm-up call.  numerics: the reference's Blackwell contract "sm100-mx" or one of the arms of
+    ops.NUMERICS (the same forward; the backward's dS block or the matched delta's normalisation differ)."""
     _check_inputs(q, k, v, causal, softmax_scale, delta_mode)
-    return _DMAttn.apply(q, k, v, causal, delta_mode)
+    ds32, norm = _numerics(numerics, q.shape[-1])
+    return _DMAttn.apply(q, k, v, causal, delta_mode, ds32, norm)
 
 
 @torch.no_grad()
-def dm_attn_debug(q, k, v, do, causal=True, mode="matched", identity=False):
+def dm_attn_debug(q, k, v, do, causal=True, mode="matched", identity=False, numerics="sm100-mx"):
     """The delta the backward consumes and the LSE it recomputes P from ("delta", "lse", (B, H, N) fp32), from the same
     producers, forward and delta path as dm_attn_func on (B, N, H, D) inputs; identity=True (matched mode) also returns
     "rowsum_dS" = sum_j dS_ij and "sum_abs_PdP" = sum_j |P_ij dP_ij| accumulated inside the backward before dS is
     quantised.  Mirrors delta_matching/sm100/attention.py:36-52."""
     qh, kh, vh, doh = (t.transpose(1, 2) for t in (q, k, v, do))
     _check_inputs(qh, kh, vh, causal, None, mode)
+    ds32, norm = _numerics(numerics, q.shape[-1])
     q8, qs, k8, ks, v8, vs, km = ops.quant_qkv(qh, kh, vh)
     o, lse = ops.fwd_fp8(q8, k8, v8, qs, ks, vs, causal)
     if mode == "matched":
         do8, dos, _ = ops.quant_do(doh, None)
-        delta = ops.delta_fp8(q8, k8, v8, do8, qs, ks, vs, dos, lse, causal)
+        delta = ops.delta_fp8(q8, k8, v8, do8, qs, ks, vs, dos, lse, causal, norm)
     else:
         do8, dos, delta = ops.quant_do(doh, o.permute(0, 2, 1, 3))
     out = {"delta": delta, "lse": lse, "o": o, "kmean": km}
     if identity:
-        _, _, _, rs, ap = ops.bwd_fp8(q8, k8, v8, do8, qs, ks, vs, dos, lse, delta, causal, identity=True)
+        _, _, _, rs, ap = ops.bwd_fp8(q8, k8, v8, do8, qs, ks, vs, dos, lse, delta, causal, identity=True, ds32=ds32)
         out["rowsum_dS"], out["sum_abs_PdP"] = rs, ap
     return out

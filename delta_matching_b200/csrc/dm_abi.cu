@@ -236,9 +236,9 @@ int dm_dbg_fwd_unordered(const void* q8, const void* k8, const void* v8, const f
   return fwd_impl(q8, k8, v8, qs, ks, vs, B, N, H, Hk, D, causal, o, o_sb, o_sn, o_sh, lse, status, stream, 1);
 }
 
-int dm_delta(const void* q8, const void* k8, const void* v8, const void* do8,
-             const float* qs, const float* ks, const float* vs, const float* dos, const float* lse,
-             int B, int N, int H, int Hk, int D, int causal, float* delta, int* status, void* stream) {
+static int delta_impl(const void* q8, const void* k8, const void* v8, const void* do8,
+                      const float* qs, const float* ks, const float* vs, const float* dos, const float* lse,
+                      int B, int N, int H, int Hk, int D, int causal, float* delta, int* status, void* stream, int norm) {
   DM_TRY(check_shape(B, N, H, Hk, D));
   DM_TRY(check_sm100());
   DM_TRY(check_device_ptr(q8, "q8")); DM_TRY(check_device_ptr(k8, "k8")); DM_TRY(check_device_ptr(v8, "v8"));
@@ -250,9 +250,21 @@ int dm_delta(const void* q8, const void* k8, const void* v8, const void* do8,
   DM_TRY(make_code_map(&tk, k8, static_cast<uint64_t>(B) * Hk * N, D));
   DM_TRY(make_code_map(&tv, v8, static_cast<uint64_t>(B) * Hk * N, D));
   DM_TRY(make_code_map(&td, do8, static_cast<uint64_t>(B) * H * N, D));
-  dm::DeltaParams p{qs, ks, vs, dos, lse, delta, B, H, Hk, N, causal ? 1 : 0, status};
+  dm::DeltaParams p{qs, ks, vs, dos, lse, delta, B, H, Hk, N, causal ? 1 : 0, status, norm};
   cudaError_t e = dm::launch_delta(D, tq, tk, tv, td, p, static_cast<cudaStream_t>(stream));
   return e == cudaSuccess ? 0 : cuda_fail(e, "matched-delta launch");
+}
+
+int dm_delta(const void* q8, const void* k8, const void* v8, const void* do8,
+             const float* qs, const float* ks, const float* vs, const float* dos, const float* lse,
+             int B, int N, int H, int Hk, int D, int causal, float* delta, int* status, void* stream) {
+  return delta_impl(q8, k8, v8, do8, qs, ks, vs, dos, lse, B, N, H, Hk, D, causal, delta, status, stream, 1);
+}
+
+int dm_delta_sum(const void* q8, const void* k8, const void* v8, const void* do8,
+                 const float* qs, const float* ks, const float* vs, const float* dos, const float* lse,
+                 int B, int N, int H, int Hk, int D, int causal, float* delta, int* status, void* stream) {
+  return delta_impl(q8, k8, v8, do8, qs, ks, vs, dos, lse, B, N, H, Hk, D, causal, delta, status, stream, 0);
 }
 
 static int bwd_impl(const void* q8, const void* k8, const void* v8, const void* do8,
@@ -264,7 +276,8 @@ static int bwd_impl(const void* q8, const void* k8, const void* v8, const void* 
                     void* dv, int64_t dv_sb, int64_t dv_sn, int64_t dv_sh,
                     float* rowsum_ds, float* sum_abs_pdp, void* workspace, int64_t workspace_bytes, int parts,
                     int* status, void* stream) {
-  if ((parts & 3) == 0 || (parts & ~3)) return fail(DM_ERR_ARG, "delta_matching: parts must be 1 (dK/dV), 2 (dQ) or 3 (got %d)", parts);
+  if ((parts & 3) == 0 || (parts & ~7))
+    return fail(DM_ERR_ARG, "delta_matching: parts must be 1 (dK/dV), 2 (dQ) or 3, plus 4 for 32 x 32 dS blocks (got %d)", parts);
   DM_TRY(check_shape(B, N, H, Hk, D));
   DM_TRY(check_sm100());
   DM_TRY(check_device_ptr(q8, "q8")); DM_TRY(check_device_ptr(k8, "k8")); DM_TRY(check_device_ptr(v8, "v8"));
@@ -290,6 +303,7 @@ static int bwd_impl(const void* q8, const void* k8, const void* v8, const void* 
   p.rowsum_ds = rowsum_ds; p.sum_abs_pdp = sum_abs_pdp;
   p.sm_scale = static_cast<float>(1.0 / sqrt(static_cast<double>(D)));
   p.B = B; p.H = H; p.Hk = Hk; p.N = N; p.causal = causal ? 1 : 0; p.status = status;
+  p.ds32 = (parts & 4) ? 1 : 0;
   CUtensorMap tds;
   if (workspace != nullptr) {
     const int64_t need = dm_bwd_workspace_bytes(B, N, H, D);
@@ -321,7 +335,7 @@ static int bwd_impl(const void* q8, const void* k8, const void* v8, const void* 
 int64_t dm_bwd_workspace_bytes(int B, int N, int H, int D) {
   if ((D != 128 && D != 256) || B <= 0 || H <= 0 || N <= 0 || (N % 128) != 0) return 0;
   const int64_t tiles = static_cast<int64_t>(B) * H * (N / 128) * (N / 128);
-  return tiles * (16384 + 4);
+  return tiles * (16384 + 16);
 }
 
 int dm_bwd_ws(const void* q8, const void* k8, const void* v8, const void* do8,

@@ -85,7 +85,10 @@ struct KvPipeCfg {
   static_assert(kSmemBytes <= 232448, "shared memory budget");
 };
 
-template <int G, int D, bool DV, bool DK>
+// DS32: the dS scale is taken per (32 queries x 32 keys), which is one warp's block of a tile (each thread holds one
+// 32-query block per tile), instead of the contract's (128 queries x 32 keys), for which the four groups' warps of a
+// key quadrant exchange their maxima.
+template <int G, int D, bool DV, bool DK, bool DS32>
 __global__ void __launch_bounds__(KvPipeCfg<G, D, DV, DK>::kThreads, 1)
 bwd_dkdv_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                      const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
@@ -93,6 +96,7 @@ bwd_dkdv_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   using C = KvPipeCfg<G, D, DV, DK>;
   constexpr int kW = C::kGroups * 4;                 // compute warps; warp kW = TMA, kW + 1 = MMA
   constexpr int CH = C::kChunks;
+  static_assert(!DS32 || CH == 1, "per-block dS scales need one 32-query block per thread and tile");
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sK = smem + C::kSmemK;
@@ -390,6 +394,7 @@ bwd_dkdv_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         continue;
       }
       // dP^T (its chain was issued when S^T was handed back) is requested while the code stores are still in flight
+      float wm = 0.f;
       if (ok) ok = wait_warp(bar_dp, ph, abort_flag);
       if (ok) {
         tc_fence_after();
@@ -424,11 +429,12 @@ bwd_dkdv_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             am1 = max3(am1, fabsf(pr[c][e + 1].x), fabsf(pr[c][e + 1].y));
           }
         }
-        const float wm = warp_max(fmaxf(am0, am1));
-        if ((tid & 31) == 0) sts_f(xch_a + 4 * (ph * 16 + warp), wm);
+        wm = warp_max(fmaxf(am0, am1));
+        if (!DS32 && (tid & 31) == 0) sts_f(xch_a + 4 * (ph * 16 + warp), wm);
       }
-      // one dS scale per (128 queries x this quadrant's 32 keys): the groups' warps of the quadrant meet here
-      bar_sync(1 + quad, 32 * C::kGroups);         // reached in every iteration, also after a failed wait
+      // one dS scale per (128 queries x this quadrant's 32 keys): the groups' warps of the quadrant meet here (reached
+      // in every iteration, also after a failed wait).  With 32 x 32 blocks the warp's own maximum is the block's.
+      if (!DS32) bar_sync(1 + quad, 32 * C::kGroups);
       const int st_cur = st;
       if (++st == C::kStages) {
         st = 0;
@@ -440,9 +446,12 @@ bwd_dkdv_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       }
       (void)st_cur;
       if (!ok) continue;
-      const uint32_t x_a = xch_a + 4 * (ph * 16 + quad);
-      float am = fmaxf(lds_f(x_a), lds_f(x_a + 16));
-      if (C::kGroups == 4) am = fmaxf(am, fmaxf(lds_f(x_a + 32), lds_f(x_a + 48)));
+      float am = wm;
+      if (!DS32) {
+        const uint32_t x_a = xch_a + 4 * (ph * 16 + quad);
+        am = fmaxf(lds_f(x_a), lds_f(x_a + 16));
+        if (C::kGroups == 4) am = fmaxf(am, fmaxf(lds_f(x_a + 32), lds_f(x_a + 48)));
+      }
       const uint32_t dsb = pow2_sb(am, 127u);
       const float ninv = -sb_to_inv(dsb);
 #pragma unroll
@@ -462,7 +471,15 @@ bwd_dkdv_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         }
       }
       if (p.ds_codes != nullptr) fence_async_smem();
-      if (p.ds_codes != nullptr && wg == 0 && (tid & 31) == 0) p.ds_words[ws_tile * 4 + quad] = static_cast<uint8_t>(dsb);
+      // scale bytes of the tile for pass 2, [query block][key block]
+      if (p.ds_codes != nullptr && (tid & 31) == 0) {
+        if (DS32) {
+          p.ds_words[ws_tile * 16 + blk0 * 4 + quad] = static_cast<uint8_t>(dsb);
+        } else if (wg == 0) {
+#pragma unroll
+          for (int qb = 0; qb < 4; ++qb) p.ds_words[ws_tile * 16 + qb * 4 + quad] = static_cast<uint8_t>(dsb);
+        }
+      }
       tmem_wait_st();
       tc_fence_before();
       __syncwarp();
@@ -690,18 +707,20 @@ bwd_dq_serial_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         }
       }
       // one scale per (this tile's 128 queries x 32 keys): reduce the block maxima over the four warps
+      // (with 32 x 32 dS blocks the warp's own maximum is the block's)
       float* red = sRed + (it & 1) * 16;
+      float wmx[4];
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
-        const float wm = warp_max(bmax[c]);
-        if ((tid & 31) == 0) red[warp * 4 + c] = wm;
+        wmx[c] = warp_max(bmax[c]);
+        if ((tid & 31) == 0) red[warp * 4 + c] = wmx[c];
       }
       bar_sync(1, 128);          // reached by every compute warp in every iteration, also after a failed wait
       if (!ok) continue;
       uint32_t sfw[4];
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
-        const float am = fmaxf(fmaxf(red[c], red[4 + c]), fmaxf(red[8 + c], red[12 + c]));
+        const float am = p.ds32 ? wmx[c] : fmaxf(fmaxf(red[c], red[4 + c]), fmaxf(red[8 + c], red[12 + c]));
         const uint32_t dsb = pow2_sb(am, 127u);
         const float inv = sb_to_inv(dsb);
         sfw[c] = sb_mul(dsb, scale_to_sb(ksv[c]));
@@ -968,6 +987,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         }
         const bool diag = p.causal && (it == qt);
         float2 v[16];
+        float wm = 0.f;
         if (ok) ok = wait_warp(bar_s, g & 1, abort_flag);
         if (ok) {
           tc_fence_after();
@@ -1006,14 +1026,15 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
             ap_acc += static_cast<double>(asum.x) + static_cast<double>(asum.y);
           }
           // one scale per (128 queries x 32 keys): the maxima of this group's four warps meet in shared memory
-          const float wm = warp_max(fmaxf(am0, am1));
+          // (with 32 x 32 dS blocks the warp's own maximum is the block's)
+          wm = warp_max(fmaxf(am0, am1));
           if ((tid & 31) == 0) sRed[(g & 1) * 16 + warp] = wm;
         }
         bar_sync(1 + wg, 128);        // reached by every warp of the group in every iteration, also after a failed wait
         if (ok && g > 0) ok = wait_warp(bar_done, (g - 1) & 1, abort_flag);   // the previous chain has read its scale words
         if (!ok) continue;
         const float* red = sRed + (g & 1) * 16 + wg * 4;
-        const uint32_t dsb = pow2_sb(fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3])), 127u);
+        const uint32_t dsb = pow2_sb(p.ds32 ? wm : fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3])), 127u);
         uint32_t w[8];
         codes32(v, sb_to_inv(dsb), w);
         // row r of the dS tile: 16-byte chunk j of the row lands at chunk (j ^ (r % 8)) (128-byte swizzle)
@@ -1083,16 +1104,16 @@ static cudaError_t set_smem(K kernel, int bytes, bool* done) {
   return cudaSuccess;
 }
 
-template <int D, bool DV, bool DK>
+template <int D, bool DV, bool DK, bool DS32>
 static cudaError_t launch_kv_pipe_t(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                                     const CUtensorMap& tdo, const CUtensorMap& tds, const BwdParams& p,
                                     cudaStream_t stream) {
   using C = KvPipeCfg<4, D, DV, DK>;
   static bool done[64] = {};
-  cudaError_t e = set_smem(bwd_dkdv_pipe_kernel<4, D, DV, DK>, C::kSmemBytes, done);
+  cudaError_t e = set_smem(bwd_dkdv_pipe_kernel<4, D, DV, DK, DS32>, C::kSmemBytes, done);
   if (e != cudaSuccess) return e;
   dim3 grid(p.N / 128, p.B * p.Hk);
-  bwd_dkdv_pipe_kernel<4, D, DV, DK><<<grid, C::kThreads, C::kSmemBytes, stream>>>(tq, tk, tv, tdo, tds, p);
+  bwd_dkdv_pipe_kernel<4, D, DV, DK, DS32><<<grid, C::kThreads, C::kSmemBytes, stream>>>(tq, tk, tv, tdo, tds, p);
   count_launch();
   return cudaGetLastError();
 }
@@ -1101,11 +1122,15 @@ cudaError_t launch_bwd_dkdv(int D, const CUtensorMap& tq, const CUtensorMap& tk,
                             const CUtensorMap& tdo, const CUtensorMap* tds_or_null, const BwdParams& p,
                             cudaStream_t stream) {
   const CUtensorMap* tds = (tds_or_null != nullptr) ? tds_or_null : &tq;     // unused by the kernel without a workspace
-  if (D == 128) return launch_kv_pipe_t<128, true, true>(tq, tk, tv, tdo, *tds, p, stream);
+  if (D == 128) {
+    return p.ds32 ? launch_kv_pipe_t<128, true, true, true>(tq, tk, tv, tdo, *tds, p, stream)
+                  : launch_kv_pipe_t<128, true, true, false>(tq, tk, tv, tdo, *tds, p, stream);
+  }
   // head_dim 256: one accumulator fills 256 of the 512 TMEM columns, so dV and dK run as two launches of the same kernel
-  cudaError_t e = launch_kv_pipe_t<256, true, false>(tq, tk, tv, tdo, *tds, p, stream);
+  cudaError_t e = launch_kv_pipe_t<256, true, false, false>(tq, tk, tv, tdo, *tds, p, stream);
   if (e != cudaSuccess) return e;
-  return launch_kv_pipe_t<256, false, true>(tq, tk, tv, tdo, *tds, p, stream);
+  return p.ds32 ? launch_kv_pipe_t<256, false, true, true>(tq, tk, tv, tdo, *tds, p, stream)
+                : launch_kv_pipe_t<256, false, true, false>(tq, tk, tv, tdo, *tds, p, stream);
 }
 
 template <int D>

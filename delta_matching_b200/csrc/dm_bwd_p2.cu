@@ -6,12 +6,13 @@
 // 16 KiB dS^T tiles and K tiles through one block-scaled MMA chain per tile, so it is bound by the L2 / HBM stream.
 //
 // Workspace: tile (head bh, query tile qt, key tile kt) at index (bh * n_t + qt) * n_t + kt holds 128 x 128 e4m3 codes
-// as [key][query] (the layout the dK chain consumes), followed after all tiles by one 32-bit word per tile whose byte j
-// is the UE8M0 scale of key block j (32 keys) of the tile.  The tile is the A operand of dQ in MN-major form
+// as [key][query] (the layout the dK chain consumes), followed after all tiles by four 32-bit words per tile: word b
+// belongs to query block b (32 queries) and its byte j is the UE8M0 scale of key block j (32 keys).  With the contract's
+// dS blocks of 128 queries x 32 keys the four words of a tile are equal; with 32 x 32 blocks they differ.  The tile is the A operand of dQ in MN-major form
 // (M = queries contiguous); K is the B operand in MN-major form as in the other kernels.
 //
 // One persistent CTA per SM, 320 threads: warps 0-3 write the per-tile scale words into TMEM (byte j = dS scale x K
-// scale of key block j, identical for all 128 rows), warps 4-7 write dQ out (at head_dim 128 two accumulators alternate
+// scale of key block j; warp b writes the word of query block b into its 32 rows), warps 4-7 write dQ out (at head_dim 128 two accumulators alternate
 // between items; at head_dim 256 one accumulator fills the columns, and an item's first chain waits for the read-out
 // of the previous item), warp 8 TMA, warp 9 MMA.  Items = (query tile, head), most key tiles first.
 #include <cuda_bf16.h>
@@ -165,7 +166,7 @@ bwd_dq_p2_kernel(const __grid_constant__ CUtensorMap tm_ds, const __grid_constan
       const int bhk = (bh / p.H) * p.Hk + (bh % p.H) / rep;
       wk.it = 0;
       wk.n_it = p.causal ? (qt + 1) : n_t;
-      wk.w_ptr = words + static_cast<size_t>(bh * n_t + qt) * n_t;
+      wk.w_ptr = words + static_cast<size_t>(bh * n_t + qt) * n_t * 4 + warp;   // this warp's query block of each tile
       wk.ks_ptr = reinterpret_cast<const float4*>(p.ks + static_cast<size_t>(bhk) * nblk);
     };
     auto walk_next = [&](Walk& wk) {
@@ -183,7 +184,7 @@ bwd_dq_p2_kernel(const __grid_constant__ CUtensorMap tm_ds, const __grid_constan
       w_q[i] = 0;
       k_q[i] = make_float4(1.f, 1.f, 1.f, 1.f);
       if (pre.item < n_items) {
-        w_q[i] = pre.w_ptr[pre.it];
+        w_q[i] = pre.w_ptr[4 * pre.it];
         k_q[i] = pre.ks_ptr[pre.it];
         walk_next(pre);
       }
@@ -201,7 +202,7 @@ bwd_dq_p2_kernel(const __grid_constant__ CUtensorMap tm_ds, const __grid_constan
           k_q[i] = k_q[i + 1];
         }
         if (pre.item < n_items) {
-          w_q[kAhead - 1] = pre.w_ptr[pre.it];
+          w_q[kAhead - 1] = pre.w_ptr[4 * pre.it];
           k_q[kAhead - 1] = pre.ks_ptr[pre.it];
           walk_next(pre);
         }

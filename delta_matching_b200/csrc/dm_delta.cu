@@ -284,7 +284,7 @@ delta_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ C
         }
         __syncwarp();
         if ((tid & 31) == 0) mbar_arrive(bar_read + slot);
-        if (ok) p.delta[static_cast<size_t>(bh) * p.N + row] = static_cast<float>(n / dd);
+        if (ok) p.delta[static_cast<size_t>(bh) * p.N + row] = static_cast<float>(p.norm ? n / dd : n);
       }
     }
     if (!ok) raise_abort(abort_flag, p.status, kStatusTimeoutCompute);

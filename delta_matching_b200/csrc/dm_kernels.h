@@ -31,6 +31,7 @@ struct DeltaParams {
   int B, H, Hk, N;
   int causal;
   int* status;
+  int norm;                    // 1: delta = sum P dP / sum P (the contract); 0: sum P dP (numerics arm "sm100-mx-nonorm")
 };
 
 struct BwdParams {
@@ -49,11 +50,12 @@ struct BwdParams {
   float* rowsum_ds;            // optional (B, H, N): sum_j dS_ij before quantisation (identity probe); may be null
   float* sum_abs_pdp;          // optional (B, H, N): sum_j |P_ij dP_ij|; may be null
   uint8_t* ds_codes;           // optional dS workspace: tile (bh, qt, kt) at ((bh n_t + qt) n_t + kt) x 16384
-  uint8_t* ds_words;           // bytes, [key][query] e4m3 codes; then per tile 4 UE8M0 bytes (one per 32-key block)
+  uint8_t* ds_words;           // bytes, [key][query] e4m3 codes; then per tile 16 UE8M0 bytes [query block][key block]
   float sm_scale;
   int B, H, Hk, N;
   int causal;
   int* status;
+  int ds32;                    // dS scale per (32 queries x 32 keys) instead of (128 x 32): numerics arm "sm100-mx-ds32"
 };
 
 struct QuantParams {

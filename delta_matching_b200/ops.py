@@ -17,6 +17,17 @@ from . import _lib
 
 E4M3 = torch.float8_e4m3fn
 BLK = 32                                  # tokens per quantisation scale
+DS_BLOCK32 = 4                            # DM_DS_BLOCK32 of include/dm_b200.h: flag bit beside the parts of the backward
+# Numerics arms: name of the reference emulation's preset (delta_matching/reference.py:613-630) -> (dS scale per
+# 32 x 32 block instead of 128 x 32, matched delta divided by sum P).  The first is the reference's Blackwell contract and
+# the default; the head_dim-256 presets name the same schemes.
+NUMERICS = {
+    "sm100-mx": (False, True),
+    "sm100-mx-d256": (False, True),
+    "sm100-mx-ds32": (True, True),
+    "sm100-mx-d256-ds32": (True, True),
+    "sm100-mx-nonorm": (False, False),
+}
 _STATUS = {}                              # device index -> int32 status word (pinned host memory the kernels write)
 _DEBUG = os.environ.get("DM_DEBUG", "0") not in ("", "0")
 
@@ -220,8 +231,9 @@ def fwd_fp8(q8, k8, v8, qs, ks, vs, causal: bool, unordered: bool = False):
     return o, lse
 
 
-def delta_fp8(q8, k8, v8, do8, qs, ks, vs, dos, lse, causal: bool):
-    """-> matched delta (B, H, N) fp32 from pass 0 of the backward.  Replaces the delta_fp8 op."""
+def delta_fp8(q8, k8, v8, do8, qs, ks, vs, dos, lse, causal: bool, norm: bool = True):
+    """-> matched delta (B, H, N) fp32 from pass 0 of the backward.  Replaces the delta_fp8 op.
+    norm=False leaves out the division by sum_j P_ij (numerics arm "sm100-mx-nonorm", see NUMERICS)."""
     dev = _cuda(q8, k8, v8, do8, qs, ks, vs, dos, lse)
     _enter(dev)
     B, H, N, D = q8.shape
@@ -231,8 +243,9 @@ def delta_fp8(q8, k8, v8, do8, qs, ks, vs, dos, lse, causal: bool):
     L = _lib.lib()
     with torch.cuda.device(dev):
         delta = torch.empty(B, H, N, device=dev, dtype=torch.float32)
-        _lib.check(L.dm_delta(_ptr(q8), _ptr(k8), _ptr(v8), _ptr(do8), _ptr(qs), _ptr(ks), _ptr(vs), _ptr(dos), _ptr(lse),
-                              B, N, H, Hk, D, int(bool(causal)), _ptr(delta), _ptr(status_word(dev)), _stream(q8)))
+        fn = L.dm_delta if norm else L.dm_delta_sum
+        _lib.check(fn(_ptr(q8), _ptr(k8), _ptr(v8), _ptr(do8), _ptr(qs), _ptr(ks), _ptr(vs), _ptr(dos), _ptr(lse),
+                      B, N, H, Hk, D, int(bool(causal)), _ptr(delta), _ptr(status_word(dev)), _stream(q8)))
         _after(dev)
     return delta
 
@@ -282,11 +295,12 @@ def plan_workspace_ranges(B: int, Hk: int, rep: int, n_t: int, group_bytes: int,
 
 
 def bwd_fp8(q8, k8, v8, do8, qs, ks, vs, dos, lse, delta, causal: bool, identity: bool = False, parts: int = 3,
-            workspace=None):
+            workspace=None, ds32: bool = False):
     """-> (dq (B, N, H, D), dk (B, N, Hk, D), dv (B, N, Hk, D)) bf16; dk / dv are already reduced over the GQA group.
     identity=True also returns (rowsum_dS, sum_abs_PdP), fp32 (B, H, N), accumulated in the kernel before dS is
     quantised.  parts: 1 = only the dK / dV kernel, 2 = only the dQ kernel, 3 = both (the outputs of a kernel that did
     not run are uninitialised).  Replaces the bwd_fp8_t op and the group fold of delta_matching/attn.py:114-117.
+    ds32=True scales dS per (32 queries x 32 keys) instead of (128 x 32) (numerics arm "sm100-mx-ds32", see NUMERICS).
 
     Without the identity probe the two-pass form runs: the dK / dV kernel leaves the dS codes in a workspace and dQ
     streams them (bit-identical to the recomputing kernel).  The workspace is allocated here unless
@@ -300,6 +314,8 @@ def bwd_fp8(q8, k8, v8, do8, qs, ks, vs, dos, lse, delta, causal: bool, identity
     for name, t in (("lse", lse), ("delta", delta)):
         _require(t.dtype == torch.float32 and tuple(t.shape) == (B, H, N) and t.is_contiguous(), f"{name} must be fp32 (B, H, N)")
     L = _lib.lib()
+    _require(parts in (1, 2, 3), "parts must be 1 (dK/dV), 2 (dQ) or 3")
+    flags = int(parts) | (DS_BLOCK32 if ds32 else 0)
     rep = H // Hk
     n_t = N // 128
     group_bytes = bwd_workspace_bytes(1, N, rep, D)
@@ -319,7 +335,7 @@ def bwd_fp8(q8, k8, v8, do8, qs, ks, vs, dos, lse, delta, causal: bool, identity
                                       _ptr(dq), dq.stride(0), dq.stride(1), dq.stride(2),
                                       _ptr(dk), dk.stride(0), dk.stride(1), dk.stride(2),
                                       _ptr(dv), dv.stride(0), dv.stride(1), dv.stride(2),
-                                      _ptr(rs), _ptr(ap), int(parts), st, _stream(q8)))
+                                      _ptr(rs), _ptr(ap), flags, st, _stream(q8)))
         else:
             if workspace is not None:
                 _require(workspace.dtype == torch.uint8 and workspace.is_contiguous() and workspace.device == dev,
@@ -344,7 +360,7 @@ def bwd_fp8(q8, k8, v8, do8, qs, ks, vs, dos, lse, delta, causal: bool, identity
                                        _ptr(v_dq), dq.stride(0), dq.stride(1), dq.stride(2),
                                        _ptr(v_dk), dk.stride(0), dk.stride(1), dk.stride(2),
                                        _ptr(v_dv), dv.stride(0), dv.stride(1), dv.stride(2),
-                                       _ptr(workspace), workspace.numel(), int(parts), st, _stream(q8)))
+                                       _ptr(workspace), workspace.numel(), flags, st, _stream(q8)))
         _after(dev)
     return (dq, dk, dv, rs, ap) if identity else (dq, dk, dv)
 

@@ -4,8 +4,8 @@ instead of ctypes calls it cannot look into.
     torch.ops.delta_matching_b200.quant_qkv(q, k, v)                     -> q8, qs, k8, ks, v8, vs, kmean
     torch.ops.delta_matching_b200.fwd_fp8(q8, k8, v8, qs, ks, vs, causal) -> O, LSE
     torch.ops.delta_matching_b200.quant_do(do, o, with_o)                -> do8, dos, delta
-    torch.ops.delta_matching_b200.delta_fp8(q8, k8, v8, do8, qs, ks, vs, dos, lse, causal) -> delta
-    torch.ops.delta_matching_b200.bwd_fp8(q8, k8, v8, do8, qs, ks, vs, dos, lse, delta, causal) -> dq, dk, dv
+    torch.ops.delta_matching_b200.delta_fp8(q8, k8, v8, do8, qs, ks, vs, dos, lse, causal, norm) -> delta
+    torch.ops.delta_matching_b200.bwd_fp8(q8, k8, v8, do8, qs, ks, vs, dos, lse, delta, causal, ds32) -> dq, dk, dv
 
 The reference registers the same roles as real ops (csrc/delta_matching_api.cpp:683-715: fwd_fp8, delta_fp8, bwd_fp8_t)
 and its autograd function calls them through torch.ops (delta_matching/attn.py:37-118), which is what lets its API run
@@ -77,28 +77,28 @@ def _(do, o, with_o):
 
 
 def _delta_fp8(q8: Tensor, k8: Tensor, v8: Tensor, do8: Tensor, qs: Tensor, ks: Tensor, vs: Tensor, dos: Tensor,
-               lse: Tensor, causal: bool) -> Tensor:
-    return ops.delta_fp8(q8, k8, v8, do8, qs, ks, vs, dos, lse, causal)
+               lse: Tensor, causal: bool, norm: bool) -> Tensor:
+    return ops.delta_fp8(q8, k8, v8, do8, qs, ks, vs, dos, lse, causal, norm)
 
 
 delta_fp8 = torch.library.custom_op(f"{NS}::delta_fp8", _delta_fp8, mutates_args=(), device_types="cuda")
 
 
 @delta_fp8.register_fake
-def _(q8, k8, v8, do8, qs, ks, vs, dos, lse, causal):
+def _(q8, k8, v8, do8, qs, ks, vs, dos, lse, causal, norm):
     return torch.empty_like(lse)
 
 
 def _bwd_fp8(q8: Tensor, k8: Tensor, v8: Tensor, do8: Tensor, qs: Tensor, ks: Tensor, vs: Tensor, dos: Tensor,
-             lse: Tensor, delta: Tensor, causal: bool) -> Tuple[Tensor, Tensor, Tensor]:
-    return ops.bwd_fp8(q8, k8, v8, do8, qs, ks, vs, dos, lse, delta, causal)
+             lse: Tensor, delta: Tensor, causal: bool, ds32: bool) -> Tuple[Tensor, Tensor, Tensor]:
+    return ops.bwd_fp8(q8, k8, v8, do8, qs, ks, vs, dos, lse, delta, causal, ds32=ds32)
 
 
 bwd_fp8 = torch.library.custom_op(f"{NS}::bwd_fp8", _bwd_fp8, mutates_args=(), device_types="cuda")
 
 
 @bwd_fp8.register_fake
-def _(q8, k8, v8, do8, qs, ks, vs, dos, lse, delta, causal):
+def _(q8, k8, v8, do8, qs, ks, vs, dos, lse, delta, causal, ds32):
     B, H, N, D = q8.shape
     Hk = k8.shape[1]
     return (q8.new_empty((B, N, H, D), dtype=BF16), q8.new_empty((B, N, Hk, D), dtype=BF16),

@@ -97,6 +97,12 @@ int dm_delta(const void* q8, const void* k8, const void* v8, const void* do8,
              const float* qs, const float* ks, const float* vs, const float* dos, const float* lse,
              int B, int N, int H, int Hk, int D, int causal, float* delta, int* status, void* stream);
 
+/* dm_delta without the division: delta_i = sum_j P_ij dP_ij.  The matched delta of the reference emulation's numerics
+ * arm "sm100-mx-nonorm" (delta_matching/reference.py:526-535 with delta_norm = False, preset at :620). */
+int dm_delta_sum(const void* q8, const void* k8, const void* v8, const void* do8,
+                 const float* qs, const float* ks, const float* vs, const float* dos, const float* lse,
+                 int B, int N, int H, int Hk, int D, int causal, float* delta, int* status, void* stream);
+
 /* Backward: dQ (H heads), dK and dV (Hk heads: the GQA group is reduced inside the kernel), bf16 with element strides
  * for (batch, token, head).  rowsum_ds / sum_abs_pdp (fp32 (B, H, N), may be NULL) receive the identity probe
  * sum_j dS_ij and sum_j |P_ij dP_ij| taken before dS is quantised.  Replaces the bwd_fp8_t op
@@ -112,7 +118,14 @@ int dm_bwd(const void* q8, const void* k8, const void* v8, const void* do8,
 
 /* dm_bwd with a choice of kernels: parts = 1 runs only the dK / dV kernel, 2 only the dQ kernel, 3 both (what dm_bwd
  * does).  The reference launches its pass 1 and pass 2 from one op (csrc/flash_bwd_fp8v10_launch.h:158-163); the split
- * exists so that each kernel can be timed and profiled alone. */
+ * exists so that each kernel can be timed and profiled alone.
+ * Adding DM_DS_BLOCK32 (4) to parts quantises dS with one power-of-two scale per (32 queries x 32 keys) instead of
+ * the contract's (128 queries x 32 keys): the reference emulation's numerics arm "sm100-mx-ds32"
+ * (delta_matching/reference.py:110-116, preset at :625; "sm100-mx-d256-ds32" at head_dim 256, :630).  Both kernels
+ * of a backward must get the same value. */
+#define DM_PARTS_DKDV 1
+#define DM_PARTS_DQ 2
+#define DM_DS_BLOCK32 4
 int dm_bwd_parts(const void* q8, const void* k8, const void* v8, const void* do8,
                  const float* qs, const float* ks, const float* vs, const float* dos,
                  const float* lse, const float* delta,

@@ -1,4 +1,5 @@
-"""CPU restatement of the reference's fp8 attention numerics (its Blackwell contract, emulation preset "sm100-mx").
+"""CPU restatement of the reference's fp8 attention numerics (its Blackwell contract, emulation preset "sm100-mx", and the
+arms "sm100-mx-ds32" and "sm100-mx-nonorm" of the same preset table).
 
 TEST INFRASTRUCTURE ONLY.  This file is the checker for the CUDA kernels: tests/, the smoke entry and the CPU-baseline
 leg of the benchmark may import it; the product package never does.  Every function restates, in its own code, what
@@ -23,7 +24,15 @@ E4M3 = torch.float8_e4m3fn
 E4M3_MAX = 448.0
 LOG2E = 1.4426950408889634
 BLK = 32          # tokens per input scale; keys per forward-P block; queries per P^T block; keys per dS block
-DS_ROWS = 128     # queries per dS block
+DS_ROWS = 128     # queries per dS block of the contract
+# numerics arm -> (queries per dS block, matched delta divided by sum P): delta_matching/reference.py:613, 620, 625, 629-630
+NUMERICS = {
+    "sm100-mx": (128, True),
+    "sm100-mx-d256": (128, True),
+    "sm100-mx-ds32": (32, True),
+    "sm100-mx-d256-ds32": (32, True),
+    "sm100-mx-nonorm": (128, False),
+}
 
 
 # ----------------------------------------------------------------------------------------------------- quantisers
@@ -95,11 +104,11 @@ def quant_rows_of_queries(P: torch.Tensor) -> torch.Tensor:
     return (to_e4m3(t / s) * s).reshape(P.shape)
 
 
-def quant_ds(dS: torch.Tensor) -> torch.Tensor:
-    """dS codes (one set for dK and dQ): power-of-two scale per (128 queries x 32 keys), all-zero block -> 1.
-    reference.py:110-116 (fake_mx2d) via scheme "mx2d:128x32"."""
+def quant_ds(dS: torch.Tensor, rows: int = DS_ROWS) -> torch.Tensor:
+    """dS codes (one set for dK and dQ): power-of-two scale per (`rows` queries x 32 keys), all-zero block -> 1.
+    reference.py:110-116 (fake_mx2d) via scheme "mx2d:128x32" (the contract) or "mx2d:32x32" (the ds32 arms)."""
     R, C = dS.shape[-2:]
-    t = dS.reshape(*dS.shape[:-2], R // DS_ROWS, DS_ROWS, C // BLK, BLK)
+    t = dS.reshape(*dS.shape[:-2], R // rows, rows, C // BLK, BLK)
     s = pow2_ceil_scale(t.abs().amax(dim=(-3, -1), keepdim=True), True)
     return (to_e4m3(t / s) * s).reshape(dS.shape)
 
@@ -142,14 +151,16 @@ def producers(q, k, v, do=None, k_mean=None):
 
 
 def dm_oracle(q, k, v, do, causal=True, mode="matched", k_mean=None, o_for_stale=None, lse_override=None, aux=False,
-              q_block=1024):
+              q_block=1024, numerics="sm100-mx"):
     """Forward + backward of the "sm100-mx" emulation.  Returns O (bf16), LSE (B, H, N) natural log, dQ / dK / dV fp32
     in the input layout, delta (B, H, N); aux=True adds rowsum_dS and sum_absPdP (fp64 sums over keys).
     reference.py:387-523 (dm_reference) restricted to preset "sm100-mx" (:612-613): forward P per (row, 32 keys),
     l from the unquantised P, backward P^T per (key, 32 queries), dS per (128 queries x 32 keys), matched
-    delta = sum P dP / sum P in fp64 (:526-535), stale delta = rowsum(dO * O) on the bf16 O (:500-501)."""
+    delta = sum P dP / sum P in fp64 (:526-535), stale delta = rowsum(dO * O) on the bf16 O (:500-501).
+    numerics: another arm of NUMERICS changes the dS block to 32 x 32 (:625, 630) or drops the division (:620)."""
     if mode not in ("matched", "stale"):
         raise ValueError(mode)
+    ds_rows, delta_norm = NUMERICS[numerics]
     B, N, H, D = q.shape
     Hk = k.shape[2]
     rep = H // Hk
@@ -205,13 +216,16 @@ def dm_oracle(q, k, v, do, causal=True, mode="matched", k_mean=None, o_for_stale
         if mode == "stale":
             dl = (do_raw[:, :, i0:i1] * O_stale[:, :, i0:i1]).sum(-1, keepdim=True)
         else:
-            dl = ((P.double() * dP.double()).sum(-1, keepdim=True) / P.double().sum(-1, keepdim=True)).float()
+            dl = (P.double() * dP.double()).sum(-1, keepdim=True)
+            if delta_norm:
+                dl = dl / P.double().sum(-1, keepdim=True)
+            dl = dl.float()
         delta[:, :, i0:i1] = dl.squeeze(-1)
         dS = P * (dP - dl)
         if aux:
             rs[:, :, i0:i1] = dS.double().sum(-1)
             ap[:, :, i0:i1] = (P.double() * dP.double()).abs().sum(-1)
-        dSq = quant_ds(dS)
+        dSq = quant_ds(dS, ds_rows)
         dK[:, :, :nk] += (dSq.transpose(-1, -2) @ Q[:, :, i0:i1]).reshape(B, Hk, rep, nk, D).sum(2)
         dQ[:, :, i0:i1] = (dSq @ K[:, :, :nk].repeat_interleave(rep, 1)) * sm
     out = {"O": Ob.transpose(1, 2), "LSE": LSE, "dQ": dQ.transpose(1, 2), "dK": dK.transpose(1, 2),

@@ -50,4 +50,5 @@ def load_golden(name):
     return out
 
 
-GOLDEN_CASES = ("c1_matched", "c1_stale", "gqa_noncausal_stale", "hd256_matched")
+GOLDEN_CASES = ("c1_matched", "c1_stale", "gqa_noncausal_stale", "hd256_matched",
+                "c1_matched_ds32", "c1_stale_ds32", "c1_matched_nonorm", "hd256_matched_ds32")

@@ -3,13 +3,14 @@
 Run where a checkout of the reference (jet-ai-projects/delta-matching) is available and pass its path (or set
 DM_REFERENCE_ROOT):
 
-    python tests/golden/make_golden.py /path/to/delta-matching
+    python tests/golden/make_golden.py /path/to/delta-matching [case ...]      (no case names: all of them)
 
 It loads delta_matching/reference.py by file path (that file has no imports besides torch), runs `dm_reference` with the
 Blackwell presets on small seeded inputs, and writes one compressed .npz per case with the inputs (bf16 bit patterns),
 the reference's producer codes and scales, and its outputs.  The reference cannot travel to the GPU machine; these files
 can.  Cases: the CPU-runnable headline configuration (B=1, N=256, H=Hk=2, D=128, causal) in both delta modes, a
-non-causal GQA stale case, and a head_dim-256 case.
+non-causal GQA stale case, and a head_dim-256 case; then the other numerics arms the kernels implement (dS scaled per
+32 x 32 block at both head dims, matched delta without the division by sum P).
 """
 import importlib.util
 import os
@@ -25,6 +26,10 @@ CASES = {
     "c1_stale": (1, 256, 2, 2, 128, True, "stale", 0, "sm100-mx"),
     "gqa_noncausal_stale": (1, 128, 2, 1, 128, False, "stale", 1, "sm100-mx"),
     "hd256_matched": (1, 128, 1, 1, 256, True, "matched", 2, "sm100-mx-d256"),
+    "c1_matched_ds32": (1, 256, 2, 2, 128, True, "matched", 0, "sm100-mx-ds32"),
+    "c1_stale_ds32": (1, 256, 2, 2, 128, True, "stale", 0, "sm100-mx-ds32"),
+    "c1_matched_nonorm": (1, 256, 2, 2, 128, True, "matched", 0, "sm100-mx-nonorm"),
+    "hd256_matched_ds32": (1, 128, 1, 1, 256, True, "matched", 2, "sm100-mx-d256-ds32"),
 }
 
 
@@ -43,10 +48,15 @@ def bits16(t):
 def main():
     root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("DM_REFERENCE_ROOT")
     if not root:
-        sys.exit("usage: make_golden.py /path/to/delta-matching   (or set DM_REFERENCE_ROOT)")
+        sys.exit("usage: make_golden.py /path/to/delta-matching [case ...]   (or set DM_REFERENCE_ROOT)")
+    only = set(sys.argv[2:])
+    if only - set(CASES):
+        sys.exit(f"unknown case(s): {sorted(only - set(CASES))}")
     R = load_reference(root)
     torch.set_num_threads(max(1, os.cpu_count() or 1))
     for name, (B, N, H, Hk, D, causal, mode, seed, preset) in CASES.items():
+        if only and name not in only:
+            continue
         g = torch.Generator(device="cpu").manual_seed(seed)
         q, k, v, do = [torch.randn(B, N, h, D, generator=g).to(torch.bfloat16) for h in (H, Hk, Hk, H)]
         r = R.dm_reference(q, k, v, do, causal, mode, preset, aux=True)

@@ -63,6 +63,6 @@ def test_parts_share_a_workspace(oracle):
 
 def test_workspace_bytes():
     from delta_matching_b200 import ops
-    assert ops.bwd_workspace_bytes(4, 4096, 32, 128) == 4 * 32 * 32 * 32 * (16384 + 4)
-    assert ops.bwd_workspace_bytes(2, 1024, 4, 256) == 2 * 4 * 8 * 8 * (16384 + 4)      # the tile does not depend on head_dim
+    assert ops.bwd_workspace_bytes(4, 4096, 32, 128) == 4 * 32 * 32 * 32 * (16384 + 16)
+    assert ops.bwd_workspace_bytes(2, 1024, 4, 256) == 2 * 4 * 8 * 8 * (16384 + 16)      # the tile does not depend on head_dim
     assert ops.bwd_workspace_bytes(2, 1000, 4, 128) == 0

@@ -31,7 +31,7 @@ def test_producers_bit_exact(case, oracle):
 def test_engine_matches_reference(case, oracle):
     g = load_golden(case)
     d = g["dims"]
-    r = oracle.dm_oracle(g["q"], g["k"], g["v"], g["do"], d["causal"], g["mode"], aux=True)
+    r = oracle.dm_oracle(g["q"], g["k"], g["v"], g["do"], d["causal"], g["mode"], aux=True, numerics=g["preset"])
     assert torch.equal(r["O"].view(torch.int16), g["O"].view(torch.int16))
     tol = 2e-6
     assert oracle.rel_l2(r["LSE"], g["LSE"]) <= tol
@@ -51,7 +51,7 @@ def test_reference_error_bounds(case, oracle):
     dQ, dK < 0.12: tests/test_dm_attn.py:15 of the reference), and the oracle reproduces the stored distances."""
     g = load_golden(case)
     d = g["dims"]
-    r = oracle.dm_oracle(g["q"], g["k"], g["v"], g["do"], d["causal"], g["mode"])
+    r = oracle.dm_oracle(g["q"], g["k"], g["v"], g["do"], d["causal"], g["mode"], numerics=g["preset"])
     ex = oracle.attention_exact(g["q"], g["k"], g["v"], g["do"], d["causal"])
     for i, (nm, bound) in enumerate((("O", 0.08), ("dQ", 0.12), ("dK", 0.12), ("dV", 0.08))):
         e = oracle.rel_l2(r[nm], ex[nm])

@@ -36,8 +36,8 @@ def test_fake_implementations_state_the_layout():
         assert _meta(do8) == _meta(q8) and _meta(dos) == _meta(qs) and none.numel() == 0
         _, _, stale = ns.quant_do(do, o.permute(0, 2, 1, 3), True)
         assert _meta(stale) == ((B, H, N), F32, "cuda")
-        delta = ns.delta_fp8(q8, k8, v8, do8, qs, ks, vs, dos, lse, True)
+        delta = ns.delta_fp8(q8, k8, v8, do8, qs, ks, vs, dos, lse, True, True)
         assert _meta(delta) == _meta(lse)
-        dq, dk, dv = ns.bwd_fp8(q8, k8, v8, do8, qs, ks, vs, dos, lse, delta, True)
+        dq, dk, dv = ns.bwd_fp8(q8, k8, v8, do8, qs, ks, vs, dos, lse, delta, True, False)
         assert _meta(dq) == ((B, N, H, D), BF16, "cuda")
         assert _meta(dk) == ((B, N, Hk, D), BF16, "cuda") and _meta(dv) == _meta(dk)

@@ -6,7 +6,7 @@ import pytest
 
 from delta_matching_b200.ops import plan_workspace_ranges
 
-TILE = 16384 + 4
+TILE = 16384 + 16
 
 
 @pytest.mark.parametrize("B,Hk,rep,n_t", [(4, 8, 4, 32), (3, 2, 2, 8), (1, 1, 8, 256), (8, 8, 8, 16)])
