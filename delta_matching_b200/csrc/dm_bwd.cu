@@ -244,7 +244,7 @@ bwd_dkdv_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         } else {
           if (!(ok = next_st())) break;                        // no dP^T in a DV launch: the region is free at once
         }
-        if (DV) {
+        if (DV && !DK) {
           if (!(ok = wait_or_abort(bar_pv, ph, abort_flag))) break;
           tc_fence_after();
           chain_acc(C::kColDv, C::kColPc, do_lo, C::kColXv, it == 0);       // dV += P^T dO
@@ -252,8 +252,12 @@ bwd_dkdv_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         if (DK) {
           if (!(ok = wait_or_abort(bar_dpfree, ph, abort_flag))) break;
           if (!(ok = next_st())) break;
+          // With both accumulators the compute warps hand P^T and dS^T codes over together (one tcgen05.wait::st and
+          // one arrival per tile instead of two): the dV chain moves behind the same barrier.  Both chains are long
+          // finished when the warps, after the exponentials of the next tile, want to overwrite the codes.
           if (!(ok = wait_or_abort(bar_pk, ph, abort_flag))) break;
           tc_fence_after();
+          if (DV) chain_acc(C::kColDv, C::kColPc, do_lo, C::kColXv, it == 0);  // dV += P^T dO
           chain_acc(C::kColDk, C::kColDc, q_lo, C::kColXk, it == 0);        // dK += dS^T Q
           if (p.ds_codes != nullptr) {
             // The compute warps also left the dS^T codes of this iteration in a staging tile: send it to the workspace.
@@ -401,12 +405,6 @@ bwd_dkdv_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         uint32_t rd[CH][32];
 #pragma unroll
         for (int c = 0; c < CH; ++c) tmem_ld32(tmem + lane_base + C::kColSd + 32 * (blk0 + c), rd[c]);
-        if (DV) {
-          tmem_wait_st();
-          tc_fence_before();
-          __syncwarp();
-          if ((tid & 31) == 0) mbar_arrive(bar_pv);
-        }
         tmem_wait_ld();
         tc_fence_before();
         __syncwarp();
