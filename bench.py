@@ -12,7 +12,7 @@ pass 0 or stale delta, backward) over one batch of synthetic input.  Workloads (
         over the ranks (strong scaling), unit u drawn from seed + u on the rank that owns it
 
 `--workload auto` (default) is c2 on one GPU and c5 on several.  With one GPU the line also carries short runs of c3, c4
-and c5 under "configs" (drop them with --no-extra).  There is no collective on the data path; after the timed region
+and c5 under "configs" and of c2 under the other numerics arms under "numerics_arms" (drop them with --no-extra).  There is no collective on the data path; after the timed region
 the ranks all_gather one 64-bit hash and one fp64 sum per unit of (O, dQ, dK, dV) for validation.
 
 Counted FLOPs per step (the metric's convention): 4 B H N^2 D forward + 2.5 x that backward, halved for causal; the
@@ -252,8 +252,9 @@ def emit(line):
 class Job:
     """One workload on this rank: inputs, the step through the public API, counted FLOPs of the whole job."""
 
-    def __init__(self, name, w, dev, rank, world, qk_scale=1.0):
+    def __init__(self, name, w, dev, rank, world, qk_scale=1.0, numerics="sm100-mx"):
         import delta_matching_b200 as dm
+        self.numerics = numerics
         from delta_matching_b200 import shard
         self.name, self.w, self.dev, self.world = name, w, dev, world
         self.dm = dm
@@ -273,7 +274,7 @@ class Job:
     def step(self):
         for t in self.leaves:
             t.grad = None
-        self.o = self.dm.dm_attn_func(*self.leaves, causal=self.w["causal"], mode=self.w["mode"])
+        self.o = self.dm.dm_attn_func(*self.leaves, causal=self.w["causal"], mode=self.w["mode"], numerics=self.numerics)
         self.o.backward(self.do)
 
     def outputs(self):
@@ -612,6 +613,14 @@ def main():
             del job
             torch.cuda.empty_cache()
             line["configs"] = {n: short_run(n, dev) for n in ("c3", "c4", "c5")}
+            # the headline workload under the other numerics arms the kernels implement (not the metric's numerics)
+            line["numerics_arms"] = {}
+            for arm in ("sm100-mx-ds32", "sm100-mx-nonorm"):
+                aj = Job(name, w, dev, 0, 1, numerics=arm)
+                ams, _ = run_timed(aj, 5, 3, torch.cuda.synchronize, lambda x: x)
+                line["numerics_arms"][arm] = {"ms_per_step": ams, "value": aj.job_flops / (ams * 1e-3) / 1e12, "unit": "TFLOPS"}
+                del aj
+            torch.cuda.empty_cache()
         if world == 1 and not args.no_cpu_baseline:
             tf, cms, cores, sample = cpu_sample(w)
             line["cpu_baseline"] = {"value": tf, "unit": "TFLOPS", "cores": cores, "kind": "port", "sample": sample,
