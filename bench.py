@@ -53,7 +53,7 @@ SEED = 1234
 # profiles/), scaled to a launch by its tile count (traffic grows with the tile count: per position one 16 KiB dS tile
 # is written for pass 2, of which about a third was still in L2 when the captured kernel ended, and the Q / dO / K / V
 # tiles are read mostly from L2).
-DKDV_DRAM_BYTES_PER_TILE = 13225.0
+DKDV_DRAM_BYTES_PER_TILE = 13148.0
 
 
 def counted_flops(B, N, H, D, causal=True):
