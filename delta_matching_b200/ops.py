@@ -287,11 +287,17 @@ def plan_workspace_ranges(B: int, Hk: int, rep: int, n_t: int, group_bytes: int,
     """(batch start, batch end, kv-group start, kv-group end) ranges of one two-pass backward call each, such that the
     dS workspace of a range (group_bytes per (batch, kv group)) stays within `cap` bytes and its tile count within the
     limit of one call: whole batches when a batch fits, else kv-group ranges of one batch (at least one group)."""
+    def even(total, fit):
+        """`total` items in the fewest ranges of at most `fit`, the ranges as equal as possible (a last range with a
+        single unit would leave most SMs idle for its whole launch)."""
+        n = -(-total // fit)
+        return [(total * i // n, total * (i + 1) // n) for i in range(n)]
+
     groups_fit = max(1, min(Hk, cap // group_bytes, _MAX_WS_TILES // (rep * n_t * n_t)))
     if groups_fit >= Hk:
         bs = max(1, min(B, cap // (group_bytes * Hk), _MAX_WS_TILES // (rep * Hk * n_t * n_t)))
-        return [(b0, min(B, b0 + bs), 0, Hk) for b0 in range(0, B, bs)]
-    return [(b, b + 1, g0, min(Hk, g0 + groups_fit)) for b in range(B) for g0 in range(0, Hk, groups_fit)]
+        return [(b0, b1, 0, Hk) for b0, b1 in even(B, bs)]
+    return [(b, b + 1, g0, g1) for b in range(B) for g0, g1 in even(Hk, groups_fit)]
 
 
 def bwd_fp8(q8, k8, v8, do8, qs, ks, vs, dos, lse, delta, causal: bool, identity: bool = False, parts: int = 3,

@@ -33,3 +33,12 @@ def test_tile_limit_splits_long_contexts():
     ranges = plan_workspace_ranges(1, 8, 4, 1024, 4 * 1024 * 1024 * TILE, 1 << 62)
     assert all((g1 - g0) * 4 * 1024 * 1024 < (1 << 24) for _, _, g0, g1 in ranges)
     assert sum(g1 - g0 for _, _, g0, g1 in ranges) == 8
+
+
+def test_ranges_are_balanced():
+    # 64 units with room for 9 per call: eight calls of eight, not seven of nine and one of one
+    group_bytes = 8 * 256 * 256 * TILE
+    ranges = plan_workspace_ranges(64, 1, 8, 256, group_bytes, 9 * group_bytes + 5)
+    assert [b1 - b0 for b0, b1, _, _ in ranges] == [8] * 8
+    ranges = plan_workspace_ranges(1, 8, 4, 32, 4 * 32 * 32 * TILE, 3 * 4 * 32 * 32 * TILE)
+    assert sorted(g1 - g0 for _, _, g0, g1 in ranges) == [2, 3, 3]
