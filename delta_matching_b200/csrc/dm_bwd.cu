@@ -48,8 +48,8 @@ __device__ __forceinline__ void store_bf16_chunk(const uint32_t (&r)[32], float 
 // every tile, 32 query columns per block; thread t % 128 = key row = TMEM lane), then one TMA warp and one MMA warp.
 // TMEM: one 128-column region is time-shared by S^T and dP^T (each is pulled into registers as soon as it lands, which
 // frees the region for the other), P^T codes, dS^T codes and the scale words have columns of their own, dV and dK
-// accumulate over all (query head of the group, query tile) iterations.  The tensor pipe therefore runs dP^T(i),
-// dV(i), S^T(i+1), dK(i) behind the exponentials of tile i.
+// accumulate over all (query head of the group, query tile) iterations.  The tensor pipe therefore runs dP^T(i) and
+// S^T(i+1) while the compute warps work on tile i, then dV(i) and dK(i) once both code sets of the tile are written.
 //
 // Head_dim 128 runs the kernel with both accumulators (DV and DK).  At head_dim 256 one accumulator fills 256 columns,
 // so the same kernel runs twice: a DV launch (S^T, P^T codes, dV: no dP^T, no dS) and a DK launch (S^T, dP^T, dS codes,
