@@ -153,9 +153,10 @@ int dm_kmean(const void* k, int64_t k_sb, int64_t k_sh, int64_t k_sn, int B, int
   return e == cudaSuccess ? 0 : cuda_fail(e, "k-mean launch");
 }
 
-int dm_quant_rows(const void* x, int64_t x_sb, int64_t x_sh, int64_t x_sn, const float* mean, float prescale,
-                  const void* o, int64_t o_sb, int64_t o_sh, int64_t o_sn, int B, int N, int H, int D,
-                  void* codes, float* scales, float* delta, void* stream) {
+// checks the arguments of one quantiser call and fills its parameter block
+static int quant_params(dm::QuantParams& p, const void* x, int64_t x_sb, int64_t x_sh, int64_t x_sn, const float* mean,
+                        float prescale, const void* o, int64_t o_sb, int64_t o_sh, int64_t o_sn, int B, int N, int H, int D,
+                        void* codes, float* scales, float* delta) {
   DM_TRY(check_shape(B, N, H, H, D));
   DM_TRY(check_device_ptr(x, "input"));
   DM_TRY(check_device_ptr(codes, "codes"));
@@ -167,7 +168,7 @@ int dm_quant_rows(const void* x, int64_t x_sb, int64_t x_sh, int64_t x_sn, const
     DM_TRY(check_device_ptr(delta, "delta"));
     DM_TRY(check_strides("o", o_sb, o_sh, o_sn));
   }
-  dm::QuantParams p{};
+  p = dm::QuantParams{};
   p.x = static_cast<const __nv_bfloat16*>(x);
   p.sb = x_sb; p.sh = x_sh; p.sn = x_sn;
   p.mean = mean;
@@ -178,6 +179,14 @@ int dm_quant_rows(const void* x, int64_t x_sb, int64_t x_sh, int64_t x_sn, const
   p.scales = scales;
   p.delta = (o != nullptr) ? delta : nullptr;
   p.B = B; p.H = H; p.N = N; p.D = D;
+  return 0;
+}
+
+int dm_quant_rows(const void* x, int64_t x_sb, int64_t x_sh, int64_t x_sn, const float* mean, float prescale,
+                  const void* o, int64_t o_sb, int64_t o_sh, int64_t o_sn, int B, int N, int H, int D,
+                  void* codes, float* scales, float* delta, void* stream) {
+  dm::QuantParams p;
+  DM_TRY(quant_params(p, x, x_sb, x_sh, x_sn, mean, prescale, o, o_sb, o_sh, o_sn, B, N, H, D, codes, scales, delta));
   cudaError_t e = dm::launch_quant(p, static_cast<cudaStream_t>(stream));
   return e == cudaSuccess ? 0 : cuda_fail(e, "quantiser launch");
 }
@@ -191,11 +200,16 @@ int dm_quant_qkv(const void* q, int64_t q_sb, int64_t q_sh, int64_t q_sn,
   DM_TRY(check_shape(B, N, H, Hk, D));
   // the softmax scale is baked into the Q codes as an fp32 multiply (delta_matching/reference.py:408)
   const float sm = static_cast<float>(1.0 / sqrt(static_cast<double>(D)));
-  DM_TRY(dm_kmean(k, k_sb, k_sh, k_sn, B, N, Hk, D, kmean, workspace, stream));
-  DM_TRY(dm_quant_rows(q, q_sb, q_sh, q_sn, nullptr, sm, nullptr, 0, 0, 0, B, N, H, D, q8, qs, nullptr, stream));
-  DM_TRY(dm_quant_rows(k, k_sb, k_sh, k_sn, kmean, 1.0f, nullptr, 0, 0, 0, B, N, Hk, D, k8, ks, nullptr, stream));
-  DM_TRY(dm_quant_rows(v, v_sb, v_sh, v_sn, nullptr, 1.0f, nullptr, 0, 0, 0, B, N, Hk, D, v8, vs, nullptr, stream));
-  return 0;
+  DM_TRY(check_device_ptr(kmean, "kmean"));
+  DM_TRY(check_device_ptr(workspace, "workspace"));
+  dm::QuantParams pq, pk, pv;
+  DM_TRY(quant_params(pq, q, q_sb, q_sh, q_sn, nullptr, sm, nullptr, 0, 0, 0, B, N, H, D, q8, qs, nullptr));
+  DM_TRY(quant_params(pk, k, k_sb, k_sh, k_sn, kmean, 1.0f, nullptr, 0, 0, 0, B, N, Hk, D, k8, ks, nullptr));
+  DM_TRY(quant_params(pv, v, v_sb, v_sh, v_sn, nullptr, 1.0f, nullptr, 0, 0, 0, B, N, Hk, D, v8, vs, nullptr));
+  dm::KMeanParams pm{static_cast<const __nv_bfloat16*>(k), k_sb, k_sh, k_sn, static_cast<float*>(workspace), kmean, B, Hk, N, D};
+  // three launches: [chunk sums of the K mean | Q | V] in one grid, the fold of the chunk sums, then K
+  cudaError_t e = dm::launch_quant_qkv(pq, pk, pv, pm, static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? 0 : cuda_fail(e, "producer launch");
 }
 
 int dm_quant_do(const void* d_o, int64_t do_sb, int64_t do_sh, int64_t do_sn,

@@ -94,6 +94,9 @@ cudaError_t launch_bwd_dq(int D, const CUtensorMap& tq, const CUtensorMap& tk, c
                           const CUtensorMap& tdo, const BwdParams& p, cudaStream_t stream);
 cudaError_t launch_bwd_dq_p2(int D, const CUtensorMap& tds, const CUtensorMap& tk, const BwdParams& p, cudaStream_t stream);
 cudaError_t launch_quant(const QuantParams& p, cudaStream_t stream);
+// Q, K, V in three launches: [K-mean chunk sums | Q | V], the fold of the chunk sums, K (pk.mean = pm.mean).
+cudaError_t launch_quant_qkv(const QuantParams& pq, const QuantParams& pk, const QuantParams& pv, const KMeanParams& pm,
+                             cudaStream_t stream);
 cudaError_t launch_kmean(const KMeanParams& p, cudaStream_t stream);
 
 }  // namespace dm

@@ -25,11 +25,14 @@ __device__ __forceinline__ void bf16x8_to_float(const uint4& v, float* f) {
 // ------------------------------------------------------------------------------------------------ K mean
 // Stage 1: one CTA per (64-token chunk, batch * kv head): column sums of the chunk, rows folded in a fixed order.
 template <int D>
-__global__ void __launch_bounds__(128) kmean_partial_kernel(const KMeanParams p) {
-  constexpr int kTpr = D / 8;            // threads per token row (16 bytes each)
-  constexpr int kRpp = 128 / kTpr;       // rows per pass
-  __shared__ float red[kRpp][D];
-  const int chunk = blockIdx.x, bh = blockIdx.y;
+struct KMeanTile {
+  static constexpr int kTpr = D / 8;            // threads per token row (16 bytes each)
+  static constexpr int kRpp = 128 / kTpr;       // rows per pass
+};
+
+template <int D>
+__device__ __forceinline__ void kmean_block(const KMeanParams& p, int chunk, int bh, float (*red)[D]) {
+  constexpr int kTpr = KMeanTile<D>::kTpr, kRpp = KMeanTile<D>::kRpp;
   const int b = bh / p.Hk, h = bh % p.Hk;
   const int tid = threadIdx.x;
   const int c8 = tid % kTpr, r0 = tid / kTpr;
@@ -52,6 +55,12 @@ __global__ void __launch_bounds__(128) kmean_partial_kernel(const KMeanParams p)
     for (int r = 1; r < kRpp; ++r) s += red[r][c];
     p.partial[(static_cast<size_t>(bh) * (p.N / 64) + chunk) * D + c] = s;
   }
+}
+
+template <int D>
+__global__ void __launch_bounds__(128) kmean_partial_kernel(const KMeanParams p) {
+  __shared__ float red[KMeanTile<D>::kRpp][D];
+  kmean_block<D>(p, blockIdx.x, blockIdx.y, red);
 }
 
 // Stage 2: one CTA per (batch, kv head): serial fold of the chunk sums in chunk order, divided by N.
@@ -84,15 +93,14 @@ cudaError_t launch_kmean(const KMeanParams& p, cudaStream_t stream) {
 }
 
 // ------------------------------------------------------------------------------------------------ quantiser
+cudaError_t launch_quant(const QuantParams& p, cudaStream_t stream);
 // kMean / kStale: the K tensor alone subtracts a mean and the dO tensor of the stale mode alone reads O; compiled out
 // elsewhere, the kernel needs fewer registers and more of its small CTAs fit an SM (more loads in flight).
 template <int D, bool kMean, bool kStale>
-__global__ void __launch_bounds__(128) quant_kernel(const QuantParams p) {
+__device__ __forceinline__ void quant_block(const QuantParams& p, int blk, int bh, float* wmax) {
   constexpr int kTpr = D / 16;           // threads per token row (16 elements each)
   constexpr int kRpp = 128 / kTpr;       // rows per pass
   constexpr int kPass = 32 / kRpp;
-  __shared__ float wmax[4];
-  const int blk = blockIdx.x, bh = blockIdx.y;
   const int b = bh / p.H, h = bh % p.H;
   const int tid = threadIdx.x;
   const int c16 = tid % kTpr, r0 = tid / kTpr;
@@ -158,6 +166,46 @@ __global__ void __launch_bounds__(128) quant_kernel(const QuantParams p) {
     w.w = cvt_e4m3x4(y[ps][12] * inv, y[ps][13] * inv, y[ps][14] * inv, y[ps][15] * inv);
     *reinterpret_cast<uint4*>(cb + static_cast<size_t>(r) * D) = w;
   }
+}
+
+template <int D, bool kMean, bool kStale>
+__global__ void __launch_bounds__(128) quant_kernel(const QuantParams p) {
+  __shared__ float wmax[4];
+  quant_block<D, kMean, kStale>(p, blockIdx.x, blockIdx.y, wmax);
+}
+
+// Q, V and the chunk sums of the K mean in one launch: the three need nothing from each other, and as separate launches
+// of a few microseconds each they spend a good part of their time filling and draining the GPU.  The grid is the
+// concatenation [K-mean chunks | Q blocks | V blocks] (the chunk sums first: the fold and the K quantiser wait for them).
+template <int D>
+__global__ void __launch_bounds__(128) quant_qv_kmean_kernel(const QuantParams pq, const QuantParams pv, const KMeanParams pk) {
+  __shared__ float wmax[4];
+  __shared__ float red[KMeanTile<D>::kRpp][D];
+  const int n_km = (pk.N / 64) * pk.B * pk.Hk;
+  const int n_q = (pq.N / 32) * pq.B * pq.H;
+  int i = static_cast<int>(blockIdx.x);
+  if (i < n_km) {
+    kmean_block<D>(pk, i % (pk.N / 64), i / (pk.N / 64), red);
+  } else if ((i -= n_km) < n_q) {
+    quant_block<D, false, false>(pq, i % (pq.N / 32), i / (pq.N / 32), wmax);
+  } else {
+    i -= n_q;
+    quant_block<D, false, false>(pv, i % (pv.N / 32), i / (pv.N / 32), wmax);
+  }
+}
+
+cudaError_t launch_quant_qkv(const QuantParams& pq, const QuantParams& pk, const QuantParams& pv, const KMeanParams& pm,
+                             cudaStream_t stream) {
+  const long long blocks = static_cast<long long>(pm.N / 64) * pm.B * pm.Hk + static_cast<long long>(pq.N / 32) * pq.B * pq.H +
+                           static_cast<long long>(pv.N / 32) * pv.B * pv.H;
+  if (blocks > 0x7fffffffll) return cudaErrorInvalidValue;
+  if (pq.D == 128) quant_qv_kmean_kernel<128><<<static_cast<unsigned>(blocks), 128, 0, stream>>>(pq, pv, pm);
+  else quant_qv_kmean_kernel<256><<<static_cast<unsigned>(blocks), 128, 0, stream>>>(pq, pv, pm);
+  kmean_fold_kernel<<<pm.B * pm.Hk, 128, 0, stream>>>(pm);
+  count_launch(2);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  return launch_quant(pk, stream);                      // K, centred by the mean that the fold has just written
 }
 
 cudaError_t launch_quant(const QuantParams& p, cudaStream_t stream) {
